@@ -12,8 +12,8 @@
   (kv heads, head size, window).  Each group has storage and a block table of its own.
   A group with a window w gives pages back as soon as no later query can read them.
 * **State** is per-slot storage of fixed size for mixers that keep a running state
-  instead of (or beside) keys and values: `state[name] [slots, *shape]`, float32, zeroed
-  when the slot is handed out.
+  instead of (or beside) keys and values: `state[name] [slots, *shape]`, float32 (or int32), zeroed
+  when the slot is handed out.  An embedding that looks back one token keeps that token here too.
 * One **padding slot** beyond the slots that are handed out, with a page and a state row of its own,
   stands in for the spare rows of a decode step whose batch size was rounded up.
 
@@ -216,8 +216,9 @@ class SequenceCache:
                 by_need.setdefault(need.kv, []).append(entry)
             if need.state is not None:
                 self.state[entry] = {
-                    name: torch.zeros((self.n_slots + 1, *shape), dtype=torch.float32, device=device)
-                    for name, shape in need.state.tensors}
+                    item[0]: torch.zeros((self.n_slots + 1, *item[1]), device=device,
+                                         dtype=torch.int32 if len(item) > 2 and item[2] == "int32" else torch.float32)
+                    for item in need.state.tensors}
         for need, entries in by_need.items():
             g = len(self.groups)
             self.groups.append(CacheGroup(need, entries, self.n_pages, self.n_slots, self.max_blocks, dtype, device))
@@ -253,7 +254,7 @@ class SequenceCache:
             index = torch.tensor(slots, dtype=torch.long, device=self.device)
             for tensors in self.state.values():
                 for t in tensors.values():
-                    t.index_fill_(0, index, 0.0)
+                    t.index_fill_(0, index, 0)
         return slots
 
     def release(self, slot: int) -> None:

@@ -2,3 +2,4 @@ from .base import (ConfigError, ModelConfig, config_from_dict, known_architectur
                    lookup_architecture, register_architecture, save_config)
 from .llama import LlamaConfig, RopeScaling
 from .kupirax import KupiraxConfig
+from .sopanex import SopanexConfig

@@ -38,6 +38,8 @@ struct LocalPrepArgs {
   float eps;
   float q_temp_coef;      // query temperature: 0 and 0 for none
   int q_temp_every;
+  int v_col;              // column of a row where the values begin: behind k, or k's own columns (values that are
+                          // the keys as projected, before norm and rotation)
 };
 
 template <typename T>
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(256) local_prepare_kernel(LocalPrepArgs a) {
   }
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     const int head = i / a.dv, e = i % a.dv;
-    ((T*)a.v_cache)[(((size_t)page * a.n_kv_heads + head) * MLL_PAGE + in_page) * a.dv + e] = row[nq + nk + i];
+    ((T*)a.v_cache)[(((size_t)page * a.n_kv_heads + head) * MLL_PAGE + in_page) * a.dv + e] = row[a.v_col + i];
   }
 }
 
@@ -137,7 +139,8 @@ struct LocalAttnArgs {
   void* out;             // [T, Hq * dv]
   int n_tokens, n_heads, n_kv_heads, d, dv, chunk, window, max_blocks;
   float scale;
-  int sink;              // 1: the softmax's denominator has one more term exp(0)
+  int sink;              // 1: the softmax's denominator has one more term exp(sink value)
+  const float* sink_values;  // [Hq] the sink's score per query head (unscaled), or null: 0
   int v_ld;              // elements between value rows: dv, or d when the values are the keys' leading columns
 };
 
@@ -182,7 +185,8 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
     q_s[g * d_pad + e] = to_float(((const T*)a.q)[((size_t)t * a.n_heads + h0 + g) * d + e]) * a.scale;
   }
   for (int i = tid; i < ng; i += 128) {
-    m_s[i] = a.sink ? 0.f : -INFINITY;  // the sink: a key that scores 0 and has no value, seen before all others
+    // the sink: a key with a score of its own and no value, seen before all others
+    m_s[i] = a.sink ? (a.sink_values ? a.sink_values[h0 + i] : 0.f) : -INFINITY;
     l_s[i] = a.sink ? 1.f : 0.f;
   }
   float acc[NACC];
@@ -346,16 +350,19 @@ MLL_API int mll_local_attention_prepare(const void* qkv, const float* q_weight, 
                                         const int* tok_seq, const int* seq_slot, const int* block_table, void* q_out,
                                         void* k_cache, void* v_cache, int dtype, int n_tokens, int ld, int n_heads,
                                         int n_kv_heads, int d, int dv, int rot, int interleaved, int max_blocks,
-                                        float eps, float q_temp_coef, int q_temp_every, cudaStream_t stream) {
+                                        float eps, float q_temp_coef, int q_temp_every, int v_from_k,
+                                        cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && d > 0 && dv > 0, "local attention prepare: bad sizes");
   MLL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "local attention prepare: %d rotated dimensions of %d", rot, d);
   MLL_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "local attention prepare: one norm weight without the other");
-  MLL_REQUIRE(ld >= n_heads * d + n_kv_heads * (d + dv), "local attention prepare: row stride %d too short", ld);
+  MLL_REQUIRE(ld >= n_heads * d + n_kv_heads * (v_from_k ? d : d + dv), "local attention prepare: row stride %d too short", ld);
+  MLL_REQUIRE(!v_from_k || dv == d, "local attention prepare: values that are the keys need dv == d, got %d / %d", dv, d);
   MLL_REQUIRE(q_temp_every >= 0, "local attention prepare: negative temperature period");
   if (n_tokens == 0) return 0;
   mll::LocalPrepArgs a{qkv, q_weight, k_weight, rot > 0 ? cos_table : nullptr, sin_table, tok_pos, tok_seq, seq_slot,
                        block_table, q_out, k_cache, v_cache, ld, n_heads, n_kv_heads, d, dv, rot, interleaved,
-                       max_blocks, eps, q_temp_coef, q_temp_every};
+                       max_blocks, eps, q_temp_coef, q_temp_every,
+                       v_from_k ? n_heads * d : n_heads * d + n_kv_heads * d};
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::local_prepare_kernel<float>), n_tokens, 256, 0, stream, a);
   else if (dtype == MLL_BF16)
@@ -369,14 +376,16 @@ MLL_API int mll_local_attention_prepare(const void* qkv, const float* q_weight, 
 MLL_API int mll_local_attention(const void* q, const void* k_cache, const void* v_cache, const int* tok_pos,
                                 const int* tok_seq, const int* seq_slot, const int* block_table, void* out, int dtype,
                                 int n_tokens, int n_heads, int n_kv_heads, int d, int dv, int chunk, int window,
-                                int max_blocks, float scale, int sink, int v_in_k, cudaStream_t stream) {
+                                int max_blocks, float scale, int sink, const float* sink_values, int v_in_k,
+                                cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention: bad head counts");
   MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0 && dv <= 1024, "local attention: head sizes %d / %d (at most 1024)", d, dv);
   MLL_REQUIRE(chunk >= 0 && window >= 0, "local attention: negative chunk or window");
   MLL_REQUIRE(!v_in_k || dv <= d, "local attention: values of %d cannot be the leading columns of keys of %d", dv, d);
   if (n_tokens == 0) return 0;
   mll::LocalAttnArgs a{q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_tokens, n_heads,
-                       n_kv_heads, d, dv, chunk, window, max_blocks, scale, sink ? 1 : 0, v_in_k ? d : dv};
+                       n_kv_heads, d, dv, chunk, window, max_blocks, scale, (sink || sink_values) ? 1 : 0, sink_values,
+                       v_in_k ? d : dv};
   if (dtype == MLL_F32) return mll::launch_local_attention<float>(a, stream);
   if (dtype == MLL_BF16) return mll::launch_local_attention<__nv_bfloat16>(a, stream);
   MLL_REQUIRE(false, "local attention: unknown dtype %d", dtype);

@@ -30,7 +30,8 @@ struct LocalMmaArgs {
   __nv_bfloat16* out;            // [T, Hq * dv]
   int n_heads, n_kv_heads, max_blocks, window, chunk, d, dv;
   float scale_log2;
-  int sink;                      // 1: one more term exp(0) in the softmax's denominator, without a value
+  int sink;                      // 1: one more term exp(sink value) in the softmax's denominator, without a value
+  const float* sink_values;      // [Hq] the sink's score per query head (natural units, unscaled), or null: 0
   int heads_as_rows;             // 1: single tokens; grid (sequences, kv heads * chunks of 64 heads of a group)
   int v_ld;                      // elements between value rows: dv, or d when the values are the keys' leading columns
   int n_splits;                  // heads_as_rows only: blocks per (sequence, kv head, head chunk) along the context
@@ -126,6 +127,13 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   // with a sink every row starts as if it had seen one key that scores 0 and has no value
   const bool sink = a.sink && (a.n_splits <= 1 || blockIdx.z == 0);
   float m_run[2] = {sink ? 0.f : -INFINITY, sink ? 0.f : -INFINITY}, l_run[2] = {sink ? 1.f : 0.f, sink ? 1.f : 0.f};
+  if (sink && a.sink_values) {  // a learned sink: the row starts at the sink's score (log2 units, like the scores)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = warp * 16 + g + 8 * r;
+      m_run[r] = a.sink_values[by_heads ? h + min(row, rows - 1) : h] * 1.4426950408889634f;
+    }
+  }
 
   for (int p = pb; p <= pe; ++p) {
     const int stage = (p - pb) & 1;
@@ -320,7 +328,8 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
                                     const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                     const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
                                     int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
-                                    int sink, int v_in_k, int heads_as_rows, int n_splits, float* scratch,
+                                    int sink, const float* sink_values, int v_in_k, int heads_as_rows, int n_splits,
+                                    float* scratch,
                                     cudaStream_t stream) {
   MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
@@ -332,7 +341,7 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
   mll::LocalMmaArgs a{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                       seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
-                      scale * 1.4426950408889634f, sink ? 1 : 0, heads_as_rows ? 1 : 0, v_in_k ? d : dv, n_splits,
+                      scale * 1.4426950408889634f, (sink || sink_values) ? 1 : 0, sink_values, heads_as_rows ? 1 : 0, v_in_k ? d : dv, n_splits,
                       scratch, scratch ? scratch + (size_t)n_tiles * n_heads * n_splits * dv : nullptr};
   if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
   if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);

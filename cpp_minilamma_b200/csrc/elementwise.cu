@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 30; }
+MLL_API int mll_abi_version() { return 31; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }
@@ -72,6 +72,53 @@ __global__ void embedding_bf16_vec8_kernel(const int* __restrict__ tokens, const
     out[2 * i] = make_float4(a.x, a.y, b.x, b.y);
     out[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
   }
+}
+
+// x[t, :] = scale * table[token[t], :] + pairs[row(t), :], row(t) a hash of the token before and the token itself:
+// (mul_prev * previous + mul_cur * token) mod buckets, and row `buckets` (the table's last) for a sequence's first
+// token.  The token before the first one of a step is the sequence's state (prev_token[slot]); the block of that
+// first token also leaves the step's last token of its sequence there for the next step.
+struct PairEmbedArgs {
+  const int* tokens;
+  const int* tok_pos;
+  const int* tok_seq;
+  const int* seq_slot;
+  const int* seq_qstart;
+  const int* seq_qlen;
+  int* prev_token;   // [slots]
+  float* x;          // [T, width]
+  int width, buckets;
+  long long mul_prev, mul_cur;
+  float scale;
+};
+
+template <typename TableT>
+__global__ void __launch_bounds__(128) embedding_pair_kernel(PairEmbedArgs a, const TableT* __restrict__ table,
+                                                             const TableT* __restrict__ pairs) {
+  __shared__ int pair_row;
+  const int t = blockIdx.x;
+  const int token = a.tokens[t];
+  if (threadIdx.x == 0) {
+    const int seq = a.tok_seq[t];
+    const int first = a.seq_qstart[seq];
+    int row = a.buckets;
+    if (a.tok_pos[t] > 0) {
+      const int before = t == first ? a.prev_token[a.seq_slot[seq]] : a.tokens[t - 1];
+      long long v = (a.mul_prev * before + a.mul_cur * token) % a.buckets;
+      row = (int)(v < 0 ? v + a.buckets : v);
+    }
+    if (t == first) a.prev_token[a.seq_slot[seq]] = a.tokens[first + a.seq_qlen[seq] - 1];  // read above, by this thread
+    pair_row = row;
+  }
+  __syncthreads();
+  const TableT* row = table + (size_t)token * a.width;
+  float* out = a.x + (size_t)t * a.width;
+  if (!pairs) {  // no pair table: the scaled row alone
+    for (int i = threadIdx.x; i < a.width; i += blockDim.x) out[i] = a.scale * to_float(row[i]);
+    return;
+  }
+  const TableT* prow = pairs + (size_t)pair_row * a.width;
+  for (int i = threadIdx.x; i < a.width; i += blockDim.x) out[i] = fmaf(a.scale, to_float(row[i]), to_float(prow[i]));
 }
 
 template <typename In, typename Out>
@@ -264,7 +311,36 @@ __global__ void heads_gate_kernel(const T* __restrict__ in, const T* __restrict_
   }
 }
 
+// out = act(in), elementwise, evaluated in float32.  kind 0: gelu in its erf form, 0.5 z (1 + erf(z / sqrt 2));
+// 1: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, int kind) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float z = to_float(in[i]);
+    const float v = kind == 0 ? 0.5f * z * (1.f + erff(z * 0.70710678118654752f))
+                              : 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    out[i] = from_float<T>(v);
+  }
+}
+
 }  // namespace mll
+
+// in, out: [n] of `dtype` (out may be in); kind: see activation_kernel.
+MLL_API int mll_activation(const void* in, void* out, int dtype, long long n, int kind, cudaStream_t stream) {
+  MLL_REQUIRE(n >= 0 && (kind == 0 || kind == 1), "activation: bad size %lld or kind %d", n, kind);
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::activation_kernel<float>), (int)blocks, 256, 0, stream, (const float*)in, (float*)out, (size_t)n, kind);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::activation_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, (const __nv_bfloat16*)in,
+               (__nv_bfloat16*)out, (size_t)n, kind);
+  else
+    MLL_REQUIRE(false, "activation: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 // dst: int32 [n]; src: int32 [n_src]; index: int32 [n].  dst and src must not overlap.
 MLL_API int mll_gather_int32(int* dst, const int* src, const int* index, int n, int n_src, cudaStream_t stream) {
@@ -314,6 +390,28 @@ MLL_API int mll_embedding(const int* tokens, const void* table, int table_dtype,
     MLL_LAUNCH((mll::embedding_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, tokens, (const __nv_bfloat16*)table, x, width);
   else
     MLL_REQUIRE(false, "embedding: unknown table dtype %d", table_dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+// tokens, tok_pos, tok_seq: int32 [n_tokens]; seq_slot, seq_qstart, seq_qlen: int32 per sequence; prev_token: int32
+// [slots]; table [vocab, width] and pairs [buckets + 1, width] of `table_dtype`; x: float32 [n_tokens, width].
+MLL_API int mll_embedding_pair(const int* tokens, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                               const int* seq_qstart, const int* seq_qlen, int* prev_token, const void* table,
+                               const void* pairs, int table_dtype, float* x, int n_tokens, int width, int buckets,
+                               long long mul_prev, long long mul_cur, float scale, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0 && buckets > 0, "pair embedding: bad sizes tokens=%d width=%d buckets=%d",
+              n_tokens, width, buckets);
+  if (n_tokens == 0) return 0;
+  mll::PairEmbedArgs a{tokens, tok_pos, tok_seq, seq_slot, seq_qstart, seq_qlen, prev_token, x, width, buckets,
+                       mul_prev, mul_cur, scale};
+  if (table_dtype == MLL_F32)
+    MLL_LAUNCH((mll::embedding_pair_kernel<float>), n_tokens, 128, 0, stream, a, (const float*)table, (const float*)pairs);
+  else if (table_dtype == MLL_BF16)
+    MLL_LAUNCH((mll::embedding_pair_kernel<__nv_bfloat16>), n_tokens, 128, 0, stream, a, (const __nv_bfloat16*)table,
+               (const __nv_bfloat16*)pairs);
+  else
+    MLL_REQUIRE(false, "pair embedding: unknown table dtype %d", table_dtype);
   MLL_LAUNCH_CHECK();
   return 0;
 }

@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 30
+ABI_VERSION = 31
 MAX_TOP_K = 1024
 
 
@@ -148,6 +148,46 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> N
         raise KernelError(f"embedding: out {tuple(out.shape)} does not fit [{n}, {width}]")
     _check(lib().mll_embedding(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
                                ctypes.c_int(n), ctypes.c_int(width), _stream()), "embedding")
+
+
+def embedding_pair(tokens, tok_pos, tok_seq, seq_slot, seq_qstart, seq_qlen, prev_token, table, pairs, out,
+                   buckets: int, mul_prev: int, mul_cur: int, scale: float) -> None:
+    """out[t, :] = scale * table[tokens[t], :] + pairs[row(t), :] (float32 [T, D]), row(t) = (mul_prev * the token
+    before + mul_cur * tokens[t]) mod buckets, and `buckets` (the table's last row) at position 0.  The token before
+    a step's first one is prev_token[slot] (int32 [slots]), where the step's last token is left for the next step.
+    `pairs` None: the scaled rows alone."""
+    _need(tokens, "pair embedding tokens", torch.int32, 1)
+    _need(table, "pair embedding table", None, 2)
+    _need(out, "pair embedding out", torch.float32, 2)
+    _need(prev_token, "pair embedding previous tokens", torch.int32, 1)
+    n, width = tokens.shape[0], table.shape[1]
+    if out.shape[0] < n or out.shape[1] != width:
+        raise KernelError(f"pair embedding: out {tuple(out.shape)} does not fit [{n}, {width}]")
+    if pairs is not None:
+        _need(pairs, "pair embedding pair table", table.dtype, 2)
+        if tuple(pairs.shape) != (buckets + 1, width):
+            raise KernelError(f"pair embedding: pair table {tuple(pairs.shape)}, expected {(buckets + 1, width)}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("seq_slot", seq_slot), ("seq_qstart", seq_qstart),
+                    ("seq_qlen", seq_qlen)):
+        _need(t, f"pair embedding {name}", torch.int32, 1)
+    _check(lib().mll_embedding_pair(_ptr(tokens), _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(seq_qstart),
+                                    _ptr(seq_qlen), _ptr(prev_token), _ptr(table), _ptr(pairs), dtype_code(table.dtype),
+                                    _ptr(out), ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(max(buckets, 1)),
+                                    ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), ctypes.c_float(scale),
+                                    _stream()), "embedding_pair")
+
+
+ACT_GELU_ERF, ACT_GELU_TANH = 0, 1
+
+
+def activation(src: torch.Tensor, dst: torch.Tensor, kind: int) -> None:
+    """dst = act(src) elementwise, evaluated in float32 (dst may be src): the erf or the tanh form of gelu."""
+    _need(src, "activation in")
+    _need(dst, "activation out", src.dtype)
+    if src.numel() != dst.numel():
+        raise KernelError("activation: sizes differ")
+    _check(lib().mll_activation(_ptr(src), _ptr(dst), dtype_code(src.dtype), ctypes.c_longlong(src.numel()),
+                                ctypes.c_int(kind), _stream()), "activation")
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -452,9 +492,20 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optio
                             ctypes.c_int(inter), ctypes.c_int(block), _stream()), "swiglu")
 
 
+class DeltaNorm(NamedTuple):
+    """What a delta passes on its way into the stream: d = scale1 * delta (+ scale2 * delta2), then, with `weight`
+    (float32 [D]), d <- d / sqrt(mean(d^2) + eps) * weight."""
+    weight: Optional[torch.Tensor]
+    eps: float = 0.0
+    scale1: float = 1.0
+    scale2: float = 1.0
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
-                eps: float, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> None:
+                eps: float, rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None,
+                delta_norm: Optional[DeltaNorm] = None) -> None:
     """x += delta (+ delta2) (float32 residual, in place); out = rmsnorm(x) * weight.
+    `delta_norm`: the delta is scaled and normalised first (see DeltaNorm), all in float32.
 
     With `rows` (int32 [n]) only those rows of x are normalised into out [n, D] and x is
     left unchanged.  `delta2`: the output of a second part that read the same norm as `delta`'s.
@@ -486,6 +537,19 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
         n_rows = x.shape[0]
     if out.shape[0] != n_rows:
         raise KernelError(f"rmsnorm: out has {out.shape[0]} rows, expected {n_rows}")
+    if delta_norm is not None:
+        if delta is None:
+            raise KernelError("rmsnorm: a norm of the delta without a delta")
+        if delta_norm.weight is not None:
+            _need(delta_norm.weight, "rmsnorm delta weight", torch.float32, 1)
+            if delta_norm.weight.shape[0] != width:
+                raise KernelError("rmsnorm: the delta's norm weight differs in width")
+        _check(lib().mll_add_normed_rmsnorm(
+            _ptr(x), _ptr(delta), _ptr(delta2), ctypes.c_float(delta_norm.scale1), ctypes.c_float(delta_norm.scale2),
+            _ptr(delta_norm.weight), ctypes.c_float(delta_norm.eps), _ptr(weight), _ptr(out), _ptr(rows),
+            dtype_code(delta_dtype), dtype_code(out.dtype), ctypes.c_int(n_rows), ctypes.c_int(width),
+            ctypes.c_float(eps), _stream()), "rmsnorm (normed delta)")
+        return
     _check(lib().mll_add2_rmsnorm(_ptr(x), _ptr(delta), _ptr(delta2), _ptr(weight), _ptr(out), _ptr(rows),
                                   dtype_code(delta_dtype), dtype_code(out.dtype), ctypes.c_int(n_rows),
                                   ctypes.c_int(width), ctypes.c_float(eps), _stream()), "rmsnorm")
@@ -924,8 +988,9 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, requ
 # --------------------------------------------------------------------------- #
 def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out,
                             k_cache, v_cache, n_heads: int, n_kv_heads: int, d: int, dv: int, rot: int,
-                            interleaved: bool, eps: float, q_temp=None) -> None:
-    """qkv [T, ld] (q heads of d, k heads of d, v heads of dv): q and k each divided by the root mean square of
+                            interleaved: bool, eps: float, q_temp=None, v_from_k: bool = False) -> None:
+    """qkv [T, ld] (q heads of d, k heads of d, v heads of dv; `v_from_k`: no v columns - the values are the keys as
+    projected, before norm and rotation, and dv == d): q and k each divided by the root mean square of
     their whole projection and multiplied by `q_weight` / `k_weight` (float32; both None: no norm), the first
     `rot` dimensions of every q and k head rotated, q to `q_out` [T, Hq * d], k and v into the cache pages
     ([pages, Hk, PAGE, d] and [pages, Hk, PAGE, dv]).  `q_temp` = (coef, every): q at position p is also
@@ -961,8 +1026,16 @@ def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq,
         _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
         dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]), ctypes.c_int(n_heads),
         ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(rot), ctypes.c_int(int(interleaved)),
-        ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), ctypes.c_float(coef), ctypes.c_int(every), _stream()),
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), ctypes.c_float(coef), ctypes.c_int(every),
+        ctypes.c_int(int(v_from_k)), _stream()),
         "local_attention_prepare")
+
+
+def _check_sink_values(sink_values, n_heads: int) -> None:
+    if sink_values is not None:
+        _need(sink_values, "local attention sink values", torch.float32, 1)
+        if sink_values.shape[0] != n_heads:
+            raise KernelError(f"local attention: {sink_values.shape[0]} sink values for {n_heads} heads")
 
 
 def _check_local_caches(k_cache, v_cache, n_kv_heads: int, d: int, dv: int, v_in_k: bool) -> None:
@@ -977,12 +1050,13 @@ def _check_local_caches(k_cache, v_cache, n_kv_heads: int, d: int, dv: int, v_in
 
 def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_heads: int, n_kv_heads: int,
                     d: int, dv: int, chunk: int, window: int, scale: float, sink: bool = False,
-                    v_in_k: bool = False) -> None:
+                    v_in_k: bool = False, sink_values: Optional[torch.Tensor] = None) -> None:
     """out [T, Hq * dv] = softmax(scale * q . k) v over the keys j <= i of the query's own chunk (j // chunk ==
     i // chunk; chunk 0: all) and window (j > i - window; 0: none); the step's own keys are in the cache already.
-    `sink`: the softmax's denominator has one more term exp(0).  `v_in_k`: the values are the leading dv columns of
-    the key rows (v_cache is k_cache)."""
+    `sink`: the softmax's denominator has one more term exp(0), or exp(sink_values[head]) with `sink_values` (float32
+    [Hq], not scaled).  `v_in_k`: the values are the leading dv columns of the key rows (v_cache is k_cache)."""
     _need(q, "local attention q", None, 2)
+    _check_sink_values(sink_values, n_heads)
     _need(out, "local attention out", q.dtype, 2)
     _need(k_cache, "local attention k cache", q.dtype, 4)
     _need(v_cache, "local attention v cache", q.dtype, 4)
@@ -994,8 +1068,8 @@ def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tok_pos), _ptr(tok_seq), _ptr(seq_slot), _ptr(block_table),
         _ptr(out), dtype_code(q.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk), ctypes.c_int(window),
-        ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)), ctypes.c_int(int(v_in_k)),
-        _stream()), "local_attention")
+        ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)), _ptr(sink_values),
+        ctypes.c_int(int(v_in_k)), _stream()), "local_attention")
 
 
 USE_TENSOR_CORE_LOCAL = True  # tests switch it off to reach the general kernel in bfloat16 prompt steps
@@ -1008,7 +1082,8 @@ def local_attention_mma_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
 
 def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                           block_table, out, n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int,
-                          scale: float, sink: bool = False, v_in_k: bool = False) -> None:
+                          scale: float, sink: bool = False, v_in_k: bool = False,
+                          sink_values: Optional[torch.Tensor] = None) -> None:
     """`local_attention` for prompt steps in bfloat16 on tensor cores: the work is a list of tiles of up to
     PREFILL_TILE query rows, (sequence, first row among the sequence's new tokens)."""
     _need(q, "local attention q", torch.bfloat16, 2)
@@ -1028,13 +1103,14 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None), _stream()), "local_attention_mma")
+        _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None), _stream()),
+        "local_attention_mma")
 
 
 def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, block_table, out, n_seqs: int,
                           n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int, scale: float,
                           sink: bool = False, v_in_k: bool = False, n_splits: int = 1,
-                          scratch: Optional[torch.Tensor] = None) -> None:
+                          scratch: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None) -> None:
     """`local_attention` for steps in which every sequence brings one token, bfloat16, on tensor cores: a block per
     (sequence, kv head) whose rows are the query heads of that kv head's group.  `n_splits` > 1: that many blocks
     along every context and a merge; `scratch` float32 of `local_attention_heads_scratch` floats."""
@@ -1054,8 +1130,8 @@ def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(seq_slot), _ptr(seq_slot), _ptr(block_table), _ptr(out), ctypes.c_int(n_seqs),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        ctypes.c_int(int(v_in_k)), ctypes.c_int(1), ctypes.c_int(n_splits), _ptr(scratch if n_splits > 1 else None),
-        _stream()), "local_attention_heads", kernels=2 if n_splits > 1 else 1)
+        _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(1), ctypes.c_int(n_splits),
+        _ptr(scratch if n_splits > 1 else None), _stream()), "local_attention_heads", kernels=2 if n_splits > 1 else 1)
 
 
 def local_attention_heads_scratch(n_seqs: int, n_heads: int, dv: int, n_splits: int) -> int:
@@ -1142,9 +1218,11 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
                n_kv_heads: int, d: int, dv: int) -> None:
     """The recurrence S <- decay S + k u^T, o = S^T q over each sequence's tokens of the step, from and to
     state [slots, H, d, dv] (float32).  With g [T, H * d] and beta [T, H]: the gated delta rule
-    (u = beta (v - S^T k) after the decay); else head_decay float32 [H] and u = v."""
+    (u = beta (v - S^T k) after the decay); with g alone: a decay per key channel and u = v; else head_decay
+    float32 [H] and u = v."""
     n = q.shape[0]
-    delta = g is not None
+    delta = g is not None and beta is not None
+    channel = g is not None and beta is None
     for name, t, width in (("q", q, n_kv_heads * d), ("k", k, n_kv_heads * d), ("v", v, n_heads * dv),
                            ("out", out, n_heads * dv)):
         _need(t, f"state scan {name}", torch.float32, 2)
@@ -1158,6 +1236,10 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
         _need(beta, "state scan beta", torch.float32, 2)
         if tuple(g.shape) != (n, n_heads * d) or tuple(beta.shape) != (n, n_heads):
             raise KernelError("state scan: g or beta of the wrong size")
+    elif channel:
+        _need(g, "state scan g", torch.float32, 2)
+        if tuple(g.shape) != (n, n_heads * d):
+            raise KernelError("state scan: g of the wrong size")
     else:
         _need(head_decay, "state scan decay", torch.float32, 1)
         if head_decay.shape[0] != n_heads:
@@ -1165,8 +1247,30 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
     _check(lib().mll_state_scan(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(head_decay), _ptr(state), _ptr(out), _ptr(seq_slot),
         _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
-        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(int(delta)), _stream()),
-        "state_scan (delta rule)" if delta else "state_scan (retention)")
+        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(1 if delta else (2 if channel else 0)), _stream()),
+        "state_scan (delta rule)" if delta else ("state_scan (channel decay)" if channel else "state_scan (retention)"))
+
+
+def channel_decay_prepare(proj, rate, bias, q, k, v, g, n_heads: int, d: int, dv: int, q_scale: float, tau: float) -> None:
+    """proj [T, ld] holds q (H * d), k (H * d), v (H * dv) side by side: q * q_scale, k and v to float32, and
+    g = sigmoid(rate + bias)^(1 / tau) per key channel (rate float32 [T, >= H * d], bias float32 [H * d] or None)."""
+    _need(proj, "channel decay proj", None, 2)
+    _need(rate, "channel decay rate", torch.float32, 2)
+    n = proj.shape[0]
+    for name, t, width in (("q", q, n_heads * d), ("k", k, n_heads * d), ("v", v, n_heads * dv), ("g", g, n_heads * d)):
+        _need(t, f"channel decay {name}", torch.float32, 2)
+        if tuple(t.shape) != (n, width):
+            raise KernelError(f"channel decay: {name} {tuple(t.shape)}, expected {(n, width)}")
+    if bias is not None:
+        _need(bias, "channel decay bias", torch.float32, 1)
+        if bias.shape[0] != n_heads * d:
+            raise KernelError("channel decay: one bias per head and key channel is needed")
+    if rate.shape[0] != n:
+        raise KernelError("channel decay: the rates have other rows than the projections")
+    _check(lib().mll_channel_decay_prepare(
+        _ptr(proj), _ptr(rate), _ptr(bias), _ptr(q), _ptr(k), _ptr(v), _ptr(g), dtype_code(proj.dtype), ctypes.c_int(n),
+        ctypes.c_int(proj.shape[1]), ctypes.c_int(rate.shape[1]), ctypes.c_int(n_heads), ctypes.c_int(d),
+        ctypes.c_int(dv), ctypes.c_float(q_scale), ctypes.c_float(tau), _stream()), "channel_decay_prepare")
 
 
 GATE_SILU, GATE_SIGMOID = 0, 1
@@ -1259,16 +1363,25 @@ def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:
     return n_pairs // rows + n_experts
 
 
-def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tensor] = None) -> None:
+def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tensor] = None, all_scores: bool = False,
+              scale: float = 1.0, gate_out: Optional[torch.Tensor] = None) -> None:
     """chosen [T, top] (int32) = the experts with the largest z = w h + bias (float32; ties: the lower index),
     weight [T, top] (float32) = softmax over the chosen logits.  `logits`: float32 [T, E] = h w^T when the caller
-    has formed the product already (a library product over many tokens)."""
+    has formed the product already (a library product over many tokens).
+    `all_scores`: s = softmax(w h) over every expert, the choice goes by s + bias, weight = the chosen s over their
+    sum (+ 1e-20), times `scale`.  `gate_out` (float32 [T]): w (and logits) have one more row behind the experts';
+    the sigmoid of its product with the token goes there."""
     _need(h, "moe route h", None, 2)
     _need(w, "moe route weight", torch.float32, 2)
     _need(chosen, "moe route chosen", torch.int32, 2)
     _need(weight, "moe route weights", torch.float32, 2)
     n, width = h.shape
-    experts = w.shape[0]
+    rows = w.shape[0]
+    experts = rows - (1 if gate_out is not None else 0)
+    if gate_out is not None:
+        _need(gate_out, "moe route gate", torch.float32, 1)
+        if gate_out.shape[0] != n:
+            raise KernelError("moe route: one gate per token is needed")
     if w.shape[1] != width or tuple(chosen.shape) != (n, top) or tuple(weight.shape) != (n, top):
         raise KernelError(f"moe route: h {tuple(h.shape)}, w {tuple(w.shape)}, chosen {tuple(chosen.shape)}")
     if bias is not None:
@@ -1277,14 +1390,16 @@ def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tenso
             raise KernelError("moe route: one bias per expert is needed")
     if logits is not None:
         _need(logits, "moe route logits", torch.float32, 2)
-        if tuple(logits.shape) != (n, experts):
-            raise KernelError(f"moe route: logits {tuple(logits.shape)}, expected {(n, experts)}")
+        if tuple(logits.shape) != (n, rows):
+            raise KernelError(f"moe route: logits {tuple(logits.shape)}, expected {(n, rows)}")
     _check(lib().mll_moe_route(_ptr(h), _ptr(w), _ptr(bias), _ptr(logits), _ptr(chosen), _ptr(weight), dtype_code(h.dtype),
-                               ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(experts), ctypes.c_int(top), _stream()),
+                               ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(experts), ctypes.c_int(top),
+                               ctypes.c_int(int(all_scores)), ctypes.c_float(scale), _ptr(gate_out), _stream()),
            "moe_route")
 
 
-def moe_sort(chosen, plan: MoePlan, n_experts: int) -> None:
+def moe_sort(chosen, plan: MoePlan, n_experts: int, n_real: Optional[int] = None) -> None:
+    """`n_real`: the experts from there on have no matrices (they hand their input on) and get no tiles."""
     n_pairs = chosen.numel()
     need = moe_max_tiles(n_pairs, n_experts, plan.rows)
     if (plan.order.numel() < n_pairs or plan.offsets.numel() < n_experts + 1 or plan.tile_expert.numel() < need
@@ -1292,7 +1407,8 @@ def moe_sort(chosen, plan: MoePlan, n_experts: int) -> None:
         raise KernelError("moe sort: the plan's arrays are too short")
     _check(lib().mll_moe_sort(_ptr(chosen), _ptr(plan.order), _ptr(plan.offsets), _ptr(plan.tile_expert),
                               _ptr(plan.tile_row0), _ptr(plan.n_tiles), ctypes.c_int(n_pairs), ctypes.c_int(n_experts),
-                              ctypes.c_int(plan.rows), _stream()), "moe_sort")
+                              ctypes.c_int(plan.rows), ctypes.c_int(n_experts if n_real is None else n_real), _stream()),
+           "moe_sort")
 
 
 def moe_mma_supported(dtype: torch.dtype, width: int, inter: int) -> bool:
@@ -1304,35 +1420,42 @@ def _plan_args(plan: MoePlan):
     return (_ptr(plan.order), _ptr(plan.offsets), _ptr(plan.tile_expert), _ptr(plan.tile_row0), _ptr(plan.n_tiles))
 
 
-def moe_gate_up(h, w, act, plan: MoePlan, top: int) -> None:
+EXPERT_SWIGLU, EXPERT_GELU = 0, 1
+
+
+def moe_gate_up(h, w, act, plan: MoePlan, top: int, form: int = EXPERT_SWIGLU, n_experts: Optional[int] = None) -> None:
     """act[place] = silu(W_gate,e h[token]) * (W_up,e h[token]); w [E, 2 I, D] holds an expert's gate rows, then
-    its up rows; act [pairs, I]."""
+    its up rows; act [pairs, I].  form EXPERT_GELU: act[place] = gelu(W_up,e h[token]) (erf form), w [E, I, D].
+    `n_experts`: the experts that the plan was sorted for, where more are routed to than have matrices."""
     _need(h, "moe gate_up h", None, 2)
     _need(w, "moe gate_up w", h.dtype, 3)
     _need(act, "moe gate_up act", h.dtype, 2)
     experts, two_inter, width = w.shape
-    inter = two_inter // 2
+    experts = experts if n_experts is None else n_experts
+    inter = two_inter // 2 if form == EXPERT_SWIGLU else two_inter
     n_pairs = h.shape[0] * top
-    if h.shape[1] != width or tuple(act.shape) != (n_pairs, inter) or two_inter != 2 * inter:
+    if h.shape[1] != width or tuple(act.shape) != (n_pairs, inter) or (form == EXPERT_SWIGLU and two_inter != 2 * inter):
         raise KernelError(f"moe gate_up: h {tuple(h.shape)}, w {tuple(w.shape)}, act {tuple(act.shape)}")
     fn = lib().mll_moe_gate_up_mma if plan.mma else lib().mll_moe_gate_up
     args = (_ptr(h), _ptr(w), _ptr(act), *_plan_args(plan))
     tiles = ctypes.c_int(moe_max_tiles(n_pairs, experts, plan.rows))
     if plan.mma:
         _check(fn(*args, tiles, ctypes.c_int(plan.rows), ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top),
-                  _stream()), "moe_gate_up_mma")
+                  ctypes.c_int(form), _stream()), "moe_gate_up_mma")
     else:
         _check(fn(*args, dtype_code(h.dtype), tiles, ctypes.c_int(width), ctypes.c_int(inter), ctypes.c_int(top),
-                  _stream()), "moe_gate_up")
+                  ctypes.c_int(form), _stream()), "moe_gate_up")
 
 
-def moe_down(act, w, y, pair_weight, plan: MoePlan, top: int) -> None:
-    """y[pair] = weight[pair] * W_down,e act[place] (float32 [pairs, D]); w [E, D, I]."""
+def moe_down(act, w, y, pair_weight, plan: MoePlan, top: int, n_experts: Optional[int] = None) -> None:
+    """y[pair] = weight[pair] * W_down,e act[place] (float32 [pairs, D]); w [E, D, I].  `n_experts`: as for
+    `moe_gate_up`."""
     _need(act, "moe down act", None, 2)
     _need(w, "moe down w", act.dtype, 3)
     _need(y, "moe down y", torch.float32, 2)
     _need(pair_weight, "moe down weights", torch.float32)
     experts, width, inter = w.shape
+    experts = experts if n_experts is None else n_experts
     n_pairs = act.shape[0]
     if act.shape[1] != inter or tuple(y.shape) != (n_pairs, width) or pair_weight.numel() != n_pairs:
         raise KernelError(f"moe down: act {tuple(act.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
@@ -1347,8 +1470,11 @@ def moe_down(act, w, y, pair_weight, plan: MoePlan, top: int) -> None:
                   _stream()), "moe_down")
 
 
-def moe_combine(y, other, out, top: int) -> None:
-    """out[t] = y[t * top] + ... + y[t * top + top - 1] (+ other[t]); y float32 [T * top, D]."""
+def moe_combine(y, other, out, top: int, chosen=None, pair_weight=None, h=None, n_real: int = 0, other_gate=None) -> None:
+    """out[t] = y[t * top] + ... + y[t * top + top - 1] (+ other[t]); y float32 [T * top, D].
+    `chosen` (int32 [T, top], with `pair_weight` float32 [T, top], `h` [T, D] of out's dtype and `n_real`): a choice of
+    an expert >= n_real adds pair_weight * h[t] instead of its row of y.  `other_gate` (float32 [T]): a factor on
+    `other`."""
     _need(y, "moe combine y", torch.float32, 2)
     _need(out, "moe combine out", None, 2)
     n, width = out.shape
@@ -1358,5 +1484,16 @@ def moe_combine(y, other, out, top: int) -> None:
         _need(other, "moe combine other", out.dtype, 2)
         if other.shape != out.shape:
             raise KernelError("moe combine: the other part's output differs in shape")
+    if chosen is not None:
+        _need(chosen, "moe combine chosen", torch.int32, 2)
+        _need(pair_weight, "moe combine weights", torch.float32, 2)
+        _need(h, "moe combine h", out.dtype, 2)
+        if tuple(chosen.shape) != (n, top) or tuple(pair_weight.shape) != (n, top) or h.shape != out.shape:
+            raise KernelError("moe combine: chosen, weights or input rows of the wrong shape")
+    if other_gate is not None:
+        _need(other_gate, "moe combine gate", torch.float32, 1)
+        if other_gate.shape[0] != n or other is None:
+            raise KernelError("moe combine: one gate per token, on the other part's output")
     _check(lib().mll_moe_combine(_ptr(y), _ptr(other), _ptr(out), dtype_code(out.dtype), ctypes.c_int(n),
-                                 ctypes.c_int(width), ctypes.c_int(top), _stream()), "moe_combine")
+                                 ctypes.c_int(width), ctypes.c_int(top), _ptr(chosen), _ptr(pair_weight), _ptr(h),
+                                 ctypes.c_int(n_real), _ptr(other_gate), _stream()), "moe_combine")

@@ -25,20 +25,33 @@
 namespace mll {
 
 // ---- route ---------------------------------------------------------------------------------------------------- //
+// How logits become choices and weights.  all_scores 0: the `top` largest logits (+ bias), softmax over those alone.
+// all_scores 1: softmax over every expert; the choice goes by score + bias, the weights are the chosen scores over
+// their sum, times `scale`.  gate_out: the router's matrix has one more row behind the experts'; the sigmoid of its
+// product with the token goes to gate_out[t] (a per-token gate of another part that reads the same rows).
+struct RouteForm {
+  int all_scores;
+  float scale;
+  float* gate_out;
+};
+
 template <typename T>
 __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w,
                                                         const float* __restrict__ bias, const float* __restrict__ logits,
                                                         int* __restrict__ chosen, float* __restrict__ weight,
-                                                        int n_tokens, int width, int n_experts, int top) {
+                                                        int n_tokens, int width, int n_experts, int top, RouteForm form) {
   extern __shared__ float z[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
+  const int n_rows = n_experts + (form.gate_out ? 1 : 0);  // the router's rows, and the row of a per-token gate behind them
+  const bool add_bias = bias && !form.all_scores;          // with scores over all experts the bias corrects the choice instead
   if (logits) {  // w h was formed elsewhere
-    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) z[e] = logits[(size_t)t * n_experts + e] + (bias ? bias[e] : 0.f);
+    for (int e = threadIdx.x; e < n_rows; e += blockDim.x)
+      z[e] = logits[(size_t)t * n_rows + e] + (add_bias && e < n_experts ? bias[e] : 0.f);
   } else {
     const T* row = h + (size_t)t * width;
     const bool vec = width % 4 == 0 && ((uintptr_t)w % 16 == 0) && ((uintptr_t)h % 16 == 0);
-    for (int e = warp; e < n_experts; e += 16) {
+    for (int e = warp; e < n_rows; e += 16) {
       const float* we = w + (size_t)e * width;
       float s[4] = {0.f, 0.f, 0.f, 0.f};  // four partial sums a lane
       if (vec) {
@@ -65,11 +78,55 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
         for (int i = lane; i < width; i += 32) s[0] = fmaf(to_float(row[i]), we[i], s[0]);
       }
       const float total = warp_sum((s[0] + s[1]) + (s[2] + s[3]));
-      if (lane == 0) z[e] = total + (bias ? bias[e] : 0.f);
+      if (lane == 0) z[e] = total + (add_bias && e < n_experts ? bias[e] : 0.f);
     }
   }
   __syncthreads();
   if (warp != 0) return;
+  if (form.gate_out && lane == 0) form.gate_out[t] = 1.f / (1.f + expf(-z[n_experts]));
+  if (form.all_scores) {
+    // scores = softmax over every expert; the choice goes by score + correction, the weights by the scores alone:
+    // weight_j = score_j / (sum of the chosen scores + 1e-20) * scale
+    float* choice = z + n_rows;  // [n_experts]
+    float top_z = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, z[e]);
+    top_z = warp_max(top_z);
+    float denom = 0.f;
+    for (int e = lane; e < n_experts; e += 32) denom += expf(z[e] - top_z);
+    denom = warp_sum(denom);
+    for (int e = lane; e < n_experts; e += 32) {
+      const float sc = expf(z[e] - top_z) / denom;
+      z[e] = sc;
+      choice[e] = sc + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    float chosen_sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int e = lane; e < n_experts; e += 32) {
+        const float v = choice[e];
+        if (v > best || (v == best && e < at)) { best = v; at = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at >= n_experts) at = j;
+      const float sc = z[at];
+      chosen_sum += sc;
+      if (lane == 0) {
+        chosen[(size_t)t * top + j] = at;
+        weight[(size_t)t * top + j] = sc;
+        choice[at] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    if (lane < top) weight[(size_t)t * top + lane] = weight[(size_t)t * top + lane] / (chosen_sum + 1e-20f) * form.scale;
+    return;
+  }
   float first = 0.f, total = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -100,7 +157,7 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
 
 // ---- sort ----------------------------------------------------------------------------------------------------- //
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ chosen, MoePlan plan, int n_pairs,
-                                                        int n_experts, int bm) {
+                                                        int n_experts, int bm, int n_real) {
   extern __shared__ int sort_smem[];
   int* counts = sort_smem;                 // [E]
   int* offsets = counts + n_experts;       // [E + 1]
@@ -115,7 +172,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     tile_off[0] = 0;
     for (int e = 0; e < n_experts; ++e) {
       offsets[e + 1] = offsets[e] + counts[e];
-      tile_off[e + 1] = tile_off[e] + (counts[e] + bm - 1) / bm;
+      // experts past n_real have no matrices (they hand their input on): places, but no tiles
+      tile_off[e + 1] = tile_off[e] + (e < n_real ? (counts[e] + bm - 1) / bm : 0);
     }
     plan.n_tiles[0] = tile_off[n_experts];
   }
@@ -159,10 +217,15 @@ __device__ __forceinline__ void load_chunk(const T* p, int n, bool vec, float* o
   }
 }
 
-// GATE_UP: A rows are the tokens of the tile's pairs, two accumulators per row (gate, up), out act[place, n].
-// otherwise: A rows are act[place], out y[pair, n] = weight[pair] * sum, float32.
-template <typename T, bool GATE_UP>
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.f + erff(z * 0.70710678118654752f)); }
+
+// KIND 1: A rows are the tokens of the tile's pairs, two accumulators per row (gate, up), out act[place, n] =
+// silu(gate) * up.  KIND 2: the same rows, one accumulator, out act[place, n] = gelu(up) (erf form).
+// KIND 0: A rows are act[place], out y[pair, n] = weight[pair] * sum, float32.
+template <typename T, int KIND>
 __global__ void __launch_bounds__(128) moe_simt_kernel(MoeProductArgs a) {
+  constexpr bool GATE_UP = KIND == 1;
+  constexpr bool GATHER = KIND != 0;
   const int tile = blockIdx.x;
   if (tile >= a.plan.n_tiles[0]) return;
   constexpr int PAD = 16 / sizeof(T);
@@ -175,7 +238,7 @@ __global__ void __launch_bounds__(128) moe_simt_kernel(MoeProductArgs a) {
   const int K = a.k, N = a.n;
   if (tid < MOE_SIMT_BM) {
     int src = -1;
-    if (tid < rows) src = GATE_UP ? a.plan.order[row0 + tid] / a.top : row0 + tid;
+    if (tid < rows) src = GATHER ? a.plan.order[row0 + tid] / a.top : row0 + tid;
     row_src[tid] = src;
   }
   __syncthreads();
@@ -218,6 +281,8 @@ __global__ void __launch_bounds__(128) moe_simt_kernel(MoeProductArgs a) {
     if (GATE_UP) {
       const float g = acc0[r];
       ((T*)a.out)[(size_t)(row0 + r) * N + col] = from_float<T>(g / (1.f + expf(-g)) * acc1[r]);
+    } else if (KIND == 2) {
+      ((T*)a.out)[(size_t)(row0 + r) * N + col] = from_float<T>(gelu_erf_f(acc0[r]));
     } else {
       const int pair = a.plan.order[row0 + r];
       ((float*)a.out)[(size_t)pair * N + col] = a.pair_weight[pair] * acc0[r];
@@ -226,15 +291,30 @@ __global__ void __launch_bounds__(128) moe_simt_kernel(MoeProductArgs a) {
 }
 
 // ---- combine -------------------------------------------------------------------------------------------------- //
+// Experts past n_real have no matrices: their share is weight * the token's own row h.  other_gate: a factor per
+// token on the other part's output.
+struct CombineExtras {
+  const int* chosen;          // [tokens, top] or null: every choice has a row in y
+  const float* pair_weight;   // [tokens, top]
+  const void* h;              // [tokens, width] of the output's dtype
+  int n_real;
+  const float* other_gate;    // [tokens] or null
+};
+
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restrict__ other, T* __restrict__ out,
-                                   size_t total, int width, int top) {
+                                   size_t total, int width, int top, CombineExtras x) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / width;
     const int c = (int)(i % width);
     float s = 0.f;
-    for (int j = 0; j < top; ++j) s += y[(t * top + j) * width + c];
-    if (other) s += to_float(other[i]);
+    for (int j = 0; j < top; ++j) {
+      if (x.chosen && x.chosen[t * top + j] >= x.n_real)
+        s += x.pair_weight[t * top + j] * to_float(((const T*)x.h)[i]);
+      else
+        s += y[(t * top + j) * width + c];
+    }
+    if (other) s += (x.other_gate ? x.other_gate[t] : 1.f) * to_float(other[i]);
     out[i] = from_float<T>(s);
   }
 }
@@ -243,23 +323,25 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const T* __restr
 
 MLL_API int mll_moe_simt_rows() { return MOE_SIMT_BM; }
 
-// h: [n_tokens, width] of `dtype`; w: float32 [n_experts, width]; bias: float32 [n_experts] or null;
-// logits: null, or float32 [n_tokens, n_experts] = h w^T formed by the caller (h and w are then not read);
+// h: [n_tokens, width] of `dtype`; w: float32 [n_experts (+ 1 with gate_out), width]; bias: float32 [n_experts] or null;
+// logits: null, or float32 [n_tokens, n_experts (+ 1)] = h w^T formed by the caller (h and w are then not read);
+// all_scores, scale, gate_out: see RouteForm;
 // chosen: int32 [n_tokens, top]; weight: float32 [n_tokens, top].
 MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, const float* logits, int* chosen,
-                          float* weight, int dtype, int n_tokens, int width, int n_experts, int top,
-                          cudaStream_t stream) {
+                          float* weight, int dtype, int n_tokens, int width, int n_experts, int top, int all_scores,
+                          float scale, float* gate_out, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
               "moe route: bad sizes tokens=%d width=%d experts=%d top=%d", n_tokens, width, n_experts, top);
   MLL_REQUIRE(n_experts <= 2048, "moe route: %d experts (at most 2048)", n_experts);
   if (n_tokens == 0) return 0;
-  const size_t smem = (size_t)n_experts * sizeof(float);
+  const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(float);
+  const mll::RouteForm form{all_scores ? 1 : 0, scale, gate_out};
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::moe_route_kernel<float>), n_tokens, 512, smem, stream, (const float*)h, w, bias, logits, chosen,
-               weight, n_tokens, width, n_experts, top);
+               weight, n_tokens, width, n_experts, top, form);
   else if (dtype == MLL_BF16)
     MLL_LAUNCH((mll::moe_route_kernel<__nv_bfloat16>), n_tokens, 512, smem, stream, (const __nv_bfloat16*)h, w, bias,
-               logits, chosen, weight, n_tokens, width, n_experts, top);
+               logits, chosen, weight, n_tokens, width, n_experts, top, form);
   else
     MLL_REQUIRE(false, "moe route: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
@@ -269,12 +351,13 @@ MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, cons
 // chosen: int32 [n_pairs]; order: int32 [n_pairs]; offsets: int32 [n_experts + 1]; tile_expert, tile_row0: int32
 // [n_pairs / bm + n_experts]; n_tiles: int32 [1].
 MLL_API int mll_moe_sort(const int* chosen, int* order, int* offsets, int* tile_expert, int* tile_row0, int* n_tiles,
-                         int n_pairs, int n_experts, int bm, cudaStream_t stream) {
+                         int n_pairs, int n_experts, int bm, int n_real, cudaStream_t stream) {
   MLL_REQUIRE(n_pairs >= 0 && n_experts > 0 && n_experts <= 2048 && bm > 0, "moe sort: bad sizes");
+  MLL_REQUIRE(n_real >= 0 && n_real <= n_experts, "moe sort: %d of %d experts have matrices", n_real, n_experts);
   if (n_pairs == 0) return 0;
   const size_t smem = (size_t)(4 * n_experts + 2) * sizeof(int);
   MLL_LAUNCH((mll::moe_sort_kernel), 1, 1024, smem, stream, chosen,
-             mll::MoePlan{order, offsets, tile_expert, tile_row0, n_tiles}, n_pairs, n_experts, bm);
+             mll::MoePlan{order, offsets, tile_expert, tile_row0, n_tiles}, n_pairs, n_experts, bm, n_real);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -285,19 +368,26 @@ static int moe_check(const char* what, int max_tiles, int k, int n, int top) {
   return 0;
 }
 
-// act[place, :] = silu(W_gate,e h[token]) * (W_up,e h[token]) for every place of the sorted pairs.
-// h: [n_tokens, width]; w: [n_experts, 2 inter, width] (an expert's gate rows, then its up rows); act: [n_pairs, inter].
+// act[place, :] = silu(W_gate,e h[token]) * (W_up,e h[token]) for every place of the sorted pairs (form 0), or
+// gelu(W_up,e h[token]) in the erf form (form 1).
+// h: [n_tokens, width]; w: [n_experts, 2 inter, width] (an expert's gate rows, then its up rows; form 1: [n_experts,
+// inter, width]); act: [n_pairs, inter].
 MLL_API int mll_moe_gate_up(const void* h, const void* w, void* act, const int* order, const int* offsets,
                             const int* tile_expert, const int* tile_row0, const int* n_tiles, int dtype, int max_tiles,
-                            int width, int inter, int top, cudaStream_t stream) {
+                            int width, int inter, int top, int form, cudaStream_t stream) {
   if (moe_check("moe gate_up", max_tiles, width, inter, top)) return -1;
+  MLL_REQUIRE(form == 0 || form == 1, "moe gate_up: unknown expert form %d", form);
   mll::MoeProductArgs a{h, w, act, nullptr, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert, (int*)tile_row0,
                                                          (int*)n_tiles}, width, inter, top};
   const dim3 grid(max_tiles, (inter + 127) / 128);
-  if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::moe_simt_kernel<float, true>), grid, 128, 0, stream, a);
+  if (dtype == MLL_F32 && form == 0)
+    MLL_LAUNCH((mll::moe_simt_kernel<float, 1>), grid, 128, 0, stream, a);
+  else if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::moe_simt_kernel<float, 2>), grid, 128, 0, stream, a);
+  else if (dtype == MLL_BF16 && form == 0)
+    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, 1>), grid, 128, 0, stream, a);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, true>), grid, 128, 0, stream, a);
+    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, 2>), grid, 128, 0, stream, a);
   else
     MLL_REQUIRE(false, "moe gate_up: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
@@ -313,9 +403,9 @@ MLL_API int mll_moe_down(const void* act, const void* w, float* y, const float* 
                                                              (int*)tile_row0, (int*)n_tiles}, inter, width, top};
   const dim3 grid(max_tiles, (width + 127) / 128);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::moe_simt_kernel<float, false>), grid, 128, 0, stream, a);
+    MLL_LAUNCH((mll::moe_simt_kernel<float, 0>), grid, 128, 0, stream, a);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, false>), grid, 128, 0, stream, a);
+    MLL_LAUNCH((mll::moe_simt_kernel<__nv_bfloat16, 0>), grid, 128, 0, stream, a);
   else
     MLL_REQUIRE(false, "moe down: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
@@ -323,19 +413,24 @@ MLL_API int mll_moe_down(const void* act, const void* w, float* y, const float* 
 }
 
 // out[t, :] = y[t * top, :] + ... + y[t * top + top - 1, :] (+ other[t, :]); y float32, other and out of `dtype`.
+// chosen (with pair_weight, h, n_real): choices of experts past n_real add pair_weight * h[t] instead of a row of y.
+// other_gate: float32 [n_tokens], a factor on `other`.
 MLL_API int mll_moe_combine(const float* y, const void* other, void* out, int dtype, int n_tokens, int width, int top,
-                            cudaStream_t stream) {
+                            const int* chosen, const float* pair_weight, const void* h, int n_real,
+                            const float* other_gate, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && width > 0 && top > 0, "moe combine: bad sizes");
+  MLL_REQUIRE(!chosen || (pair_weight && h), "moe combine: pass-through experts need the weights and the input rows");
+  const mll::CombineExtras extras{chosen, pair_weight, h, n_real, other_gate};
   if (n_tokens == 0) return 0;
   const size_t total = (size_t)n_tokens * width;
   long long blocks = (long long)((total + 255) / 256);
   if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::moe_combine_kernel<float>), (int)blocks, 256, 0, stream, y, (const float*)other, (float*)out, total,
-               width, top);
+               width, top, extras);
   else if (dtype == MLL_BF16)
     MLL_LAUNCH((mll::moe_combine_kernel<__nv_bfloat16>), (int)blocks, 256, 0, stream, y, (const __nv_bfloat16*)other,
-               (__nv_bfloat16*)out, total, width, top);
+               (__nv_bfloat16*)out, total, width, top, extras);
   else
     MLL_REQUIRE(false, "moe combine: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

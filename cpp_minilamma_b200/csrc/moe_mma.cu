@@ -31,8 +31,12 @@ struct MoeMmaShape {
 using MoeMmaWide = MoeMmaShape<2, 8, 4, 2, 64, 3>;   // 128 rows x 128 weight rows: prompts
 using MoeMmaSmall = MoeMmaShape<1, 2, 1, 4, 64, 4>;  // 16 rows x 64 weight rows: single tokens
 
-template <bool GATE_UP, int MT, int NT, int WM, int WN, int MMA_BK, int MMA_STAGES>
+// KIND 0: down; 1: gate_up (silu(gate) * up); 2: up alone with gelu (erf form) - the layout of `down`, rows gathered
+// by token, the activation in the accumulators, bfloat16 out by place.
+template <int KIND, int MT, int NT, int WM, int WN, int MMA_BK, int MMA_STAGES>
 __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a) {
+  constexpr bool GATE_UP = KIND == 1;
+  constexpr bool GATHER = KIND != 0;
   using Shape = MoeMmaShape<MT, NT, WM, WN, MMA_BK, MMA_STAGES>;
   static_assert(NT % 2 == 0, "a warp's 8-column tiles come in pairs");
   constexpr int BM = Shape::BM, BN = Shape::BN, MMA_LD = Shape::LD, MMA_THREADS = Shape::THREADS;
@@ -51,7 +55,7 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
   const int rows = min(BM, a.plan.offsets[e + 1] - row0);
   const int K = a.k, N = a.n;
   const int n0 = blockIdx.y * (GATE_UP ? BN / 2 : BN);  // first activation column (gate_up) or output column (down)
-  if (tid < BM) row_src[tid] = tid < rows ? (GATE_UP ? a.plan.order[row0 + tid] / a.top : row0 + tid) : -1;
+  if (tid < BM) row_src[tid] = tid < rows ? (GATHER ? a.plan.order[row0 + tid] / a.top : row0 + tid) : -1;
   __syncthreads();
   const __nv_bfloat16* act = (const __nv_bfloat16*)a.a;
   const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)e * (GATE_UP ? 2 * N : N) * K;
@@ -138,6 +142,17 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
           *reinterpret_cast<__nv_bfloat162*>(dst + col) =
               __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
         }
+      } else if (KIND == 2) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)a.out + (size_t)place * N;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          const int col = n0 + wn * NT * 8 + n * 8 + 2 * t;
+          if (col >= N) continue;
+          const float u0 = acc[m][n][2 * half], u1 = acc[m][n][2 * half + 1];
+          *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+              __floats2bfloat162_rn(0.5f * u0 * (1.f + erff(u0 * 0.70710678118654752f)),
+                                    0.5f * u1 * (1.f + erff(u1 * 0.70710678118654752f)));
+        }
       } else {
         const int pair = a.plan.order[place];
         const float pw = a.pair_weight[pair];
@@ -152,10 +167,11 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(MoeProductArgs a)
     }
 }
 
-template <bool GATE_UP, int MT, int NT, int WM, int WN, int BK, int STAGES>
+template <int KIND, int MT, int NT, int WM, int WN, int BK, int STAGES>
 int launch_moe_mma(const MoeProductArgs& a, int max_tiles, cudaStream_t stream) {
   using Shape = MoeMmaShape<MT, NT, WM, WN, BK, STAGES>;
-  auto kernel = moe_mma_kernel<GATE_UP, MT, NT, WM, WN, BK, STAGES>;
+  constexpr bool GATE_UP = KIND == 1;
+  auto kernel = moe_mma_kernel<KIND, MT, NT, WM, WN, BK, STAGES>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::SMEM);
   if (err != cudaSuccess) {
     mll_set_error("moe (mma): cannot reserve %zu bytes of shared memory: %s", Shape::SMEM, cudaGetErrorString(err));
@@ -167,10 +183,10 @@ int launch_moe_mma(const MoeProductArgs& a, int max_tiles, cudaStream_t stream) 
   return 0;
 }
 
-template <bool GATE_UP>
+template <int KIND>
 int launch_moe_mma_rows(const MoeProductArgs& a, int max_tiles, int tile_rows, cudaStream_t stream) {
-  if (tile_rows == MoeMmaWide::BM) return launch_moe_mma<GATE_UP, 2, 8, 4, 2, 64, 3>(a, max_tiles, stream);
-  if (tile_rows == MoeMmaSmall::BM) return launch_moe_mma<GATE_UP, 1, 2, 1, 4, 64, 4>(a, max_tiles, stream);
+  if (tile_rows == MoeMmaWide::BM) return launch_moe_mma<KIND, 2, 8, 4, 2, 64, 3>(a, max_tiles, stream);
+  if (tile_rows == MoeMmaSmall::BM) return launch_moe_mma<KIND, 1, 2, 1, 4, 64, 4>(a, max_tiles, stream);
   mll_set_error("moe (mma): tiles of %d rows (known: %d, %d)", tile_rows, MoeMmaSmall::BM, MoeMmaWide::BM);
   return -1;
 }
@@ -185,12 +201,14 @@ MLL_API int mll_moe_mma_supported(int width, int inter) { return width > 0 && in
 
 MLL_API int mll_moe_gate_up_mma(const void* h, const void* w, void* act, const int* order, const int* offsets,
                                 const int* tile_expert, const int* tile_row0, const int* n_tiles, int max_tiles,
-                                int tile_rows, int width, int inter, int top, cudaStream_t stream) {
+                                int tile_rows, int width, int inter, int top, int form, cudaStream_t stream) {
+  MLL_REQUIRE(form == 0 || form == 1, "moe gate_up (mma): unknown expert form %d", form);
   MLL_REQUIRE(mll_moe_mma_supported(width, inter) && max_tiles > 0 && top > 0, "moe gate_up (mma): sizes %d / %d", width, inter);
   MLL_REQUIRE((inter + 31) / 32 <= 65535, "moe gate_up (mma): %d columns are too many for one launch", inter);
   mll::MoeProductArgs a{h, w, act, nullptr, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert, (int*)tile_row0,
                                                          (int*)n_tiles}, width, inter, top};
-  return mll::launch_moe_mma_rows<true>(a, max_tiles, tile_rows, stream);
+  if (form == 1) return mll::launch_moe_mma_rows<2>(a, max_tiles, tile_rows, stream);
+  return mll::launch_moe_mma_rows<1>(a, max_tiles, tile_rows, stream);
 }
 
 MLL_API int mll_moe_down_mma(const void* act, const void* w, float* y, const float* pair_weight, const int* order,
@@ -200,5 +218,5 @@ MLL_API int mll_moe_down_mma(const void* act, const void* w, float* y, const flo
   MLL_REQUIRE((width + 63) / 64 <= 65535, "moe down (mma): %d columns are too many for one launch", width);
   mll::MoeProductArgs a{act, w, y, pair_weight, mll::MoePlan{(int*)order, (int*)offsets, (int*)tile_expert,
                                                              (int*)tile_row0, (int*)n_tiles}, inter, width, top};
-  return mll::launch_moe_mma_rows<false>(a, max_tiles, tile_rows, stream);
+  return mll::launch_moe_mma_rows<0>(a, max_tiles, tile_rows, stream);
 }

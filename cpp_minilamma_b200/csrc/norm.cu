@@ -10,6 +10,14 @@
 
 namespace mll {
 
+// What happens to the delta on its way into the stream: delta = scale1 * delta (+ scale2 * delta2), and with a
+// weight the delta is normalised by its own root mean square first: x += delta / sqrt(mean(delta^2) + eps) * weight
+// (a block whose sub-layers end in a norm of their own).
+struct DeltaNorm {
+  const float* weight;  // [width] or null: the delta is added as it is
+  float eps, scale1, scale2;
+};
+
 // One block per output row.  The row (after the add) is kept in shared memory between
 // the two passes.  `rows` (optional) selects which rows of x are normalised: output row
 // r reads x row rows[r]; the residual add is then not written back to x.
@@ -17,7 +25,7 @@ template <typename DeltaT, typename OutT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                                    const DeltaT* __restrict__ delta2,
                                    const float* __restrict__ weight, OutT* __restrict__ out,
-                                   const int* __restrict__ rows, int width, float eps) {
+                                   const int* __restrict__ rows, int width, float eps, DeltaNorm dn) {
   extern __shared__ float row_buf[];
   __shared__ float scratch[32];
   const int r = blockIdx.x;
@@ -25,11 +33,21 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const DeltaT* __restri
   float* xr = x + (size_t)src * width;
   const DeltaT* dr = delta ? delta + (size_t)src * width : nullptr;
   const DeltaT* dr2 = delta2 ? delta2 + (size_t)src * width : nullptr;
+  float fd = 1.f;
+  if (dr && dn.weight) {  // the delta passes a norm of its own before it joins the stream
+    float sd = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      const float d = dr2 ? dn.scale1 * to_float(dr[i]) + dn.scale2 * to_float(dr2[i]) : dn.scale1 * to_float(dr[i]);
+      sd += d * d;
+    }
+    fd = 1.f / sqrtf(block_sum(sd, scratch) / (float)width + dn.eps);
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = xr[i];
     if (dr) {
-      v += dr2 ? to_float(dr[i]) + to_float(dr2[i]) : to_float(dr[i]);
+      const float d = dr2 ? dn.scale1 * to_float(dr[i]) + dn.scale2 * to_float(dr2[i]) : dn.scale1 * to_float(dr[i]);
+      v += dn.weight ? d * fd * dn.weight[i] : d;
       if (!rows) xr[i] = v;
     }
     row_buf[i] = v;
@@ -72,7 +90,7 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
                        const DeltaT* __restrict__ delta2,
                        const float* __restrict__ weight, OutT* __restrict__ out,
-                       const int* __restrict__ rows, int width, float eps) {
+                       const int* __restrict__ rows, int width, float eps, DeltaNorm dn) {
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -95,9 +113,29 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
       const int g = threadIdx.x + k * 256;
       if (g < groups) {
         dl[k] = load4<DeltaT>(dr + 4 * g);
+        if (dn.scale1 != 1.f) { dl[k].x *= dn.scale1; dl[k].y *= dn.scale1; dl[k].z *= dn.scale1; dl[k].w *= dn.scale1; }
         if (delta2) {  // the outputs of two parts that read the same norm: their sum first, then the stream
           const float4 d2 = load4<DeltaT>(delta2 + (size_t)src * width + 4 * g);
-          dl[k].x += d2.x; dl[k].y += d2.y; dl[k].z += d2.z; dl[k].w += d2.w;
+          dl[k].x = fmaf(dn.scale2, d2.x, dl[k].x); dl[k].y = fmaf(dn.scale2, d2.y, dl[k].y);
+          dl[k].z = fmaf(dn.scale2, d2.z, dl[k].z); dl[k].w = fmaf(dn.scale2, d2.w, dl[k].w);
+        }
+      }
+    }
+    if (dn.weight) {  // the delta's own norm (uniform over the block: every thread takes part in the sum)
+      float sd = 0.f;
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int g = threadIdx.x + k * 256;
+        if (g < groups) sd += dl[k].x * dl[k].x + dl[k].y * dl[k].y + dl[k].z * dl[k].z + dl[k].w * dl[k].w;
+      }
+      const float fd = 1.f / sqrtf(block_sum(sd, scratch) / (float)width + dn.eps);
+      __syncthreads();  // scratch is used again below
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int g = threadIdx.x + k * 256;
+        if (g < groups) {
+          const float4 dw = load4<float>(dn.weight + 4 * g);
+          dl[k].x *= fd * dw.x; dl[k].y *= fd * dw.y; dl[k].z *= fd * dw.z; dl[k].w *= fd * dw.w;
         }
       }
     }
@@ -130,21 +168,21 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const DeltaT* __restrict__ delta,
 
 template <typename DeltaT, typename OutT>
 int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, const float* weight, void* out,
-                       const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
+                       const int* rows, int n_rows, int width, float eps, DeltaNorm dn, cudaStream_t stream) {
   const bool aligned = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
                        ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 8 == 0) &&
-                       (!delta2 || (uintptr_t)delta2 % 8 == 0);
+                       (!delta2 || (uintptr_t)delta2 % 8 == 0) && (!dn.weight || (uintptr_t)dn.weight % 16 == 0);
   if (aligned && width <= 4 * 256 * 8) {
     const int groups = width / 4;
     if (groups <= 256 * 2)
       MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 2>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
-                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps, dn);
     else if (groups <= 256 * 4)
       MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 4>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
-                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps, dn);
     else
       MLL_LAUNCH((add_rmsnorm_vec_kernel<DeltaT, OutT, 8>), n_rows, 256, 0, stream, x, (const DeltaT*)delta,
-                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps);
+                 (const DeltaT*)delta2, weight, (OutT*)out, rows, width, eps, dn);
     MLL_LAUNCH_CHECK();
     return 0;
   }
@@ -159,7 +197,7 @@ int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, const fl
     }
   }
   MLL_LAUNCH((kernel), n_rows, threads, smem, stream, x, (const DeltaT*)delta, (const DeltaT*)delta2, weight,
-             (OutT*)out, rows, width, eps);
+             (OutT*)out, rows, width, eps, dn);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -330,6 +368,11 @@ MLL_API int mll_apply_row_norm(const void* values, const float* sumsq, int parti
   return 0;
 }
 
+MLL_API int mll_add_normed_rmsnorm(float* x, const void* delta, const void* delta2, float scale1, float scale2,
+                                   const float* delta_weight, float delta_eps, const float* weight, void* out,
+                                   const int* rows, int delta_dtype, int out_dtype, int n_rows, int width, float eps,
+                                   cudaStream_t stream);
+
 // x: float32 [*, width] residual stream; delta, delta2: optional [*, width] of `delta_dtype` (delta2 only with
 // delta: the outputs of two parts that read the same norm); weight: float32 [width]; out: [n_rows, width] of
 // `out_dtype`; rows: optional int32 [n_rows] gather list.  out may be x itself (float32): a block reads its
@@ -337,19 +380,33 @@ MLL_API int mll_apply_row_norm(const void* values, const float* sumsq, int parti
 MLL_API int mll_add2_rmsnorm(float* x, const void* delta, const void* delta2, const float* weight, void* out,
                              const int* rows, int delta_dtype, int out_dtype, int n_rows, int width, float eps,
                              cudaStream_t stream) {
+  return mll_add_normed_rmsnorm(x, delta, delta2, 1.f, 1.f, nullptr, 0.f, weight, out, rows, delta_dtype, out_dtype,
+                                n_rows, width, eps, stream);
+}
+
+// As mll_add2_rmsnorm with the delta scaled and normalised on its way into the stream:
+//   d = scale1 * delta (+ scale2 * delta2);  with delta_weight: d <- d / sqrt(mean(d^2) + delta_eps) * delta_weight;
+//   x += d;  out = x / sqrt(mean(x^2) + eps) * weight.   All of it float32.
+MLL_API int mll_add_normed_rmsnorm(float* x, const void* delta, const void* delta2, float scale1, float scale2,
+                                   const float* delta_weight, float delta_eps, const float* weight, void* out,
+                                   const int* rows, int delta_dtype, int out_dtype, int n_rows, int width, float eps,
+                                   cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes rows=%d width=%d", n_rows, width);
+  MLL_REQUIRE(delta || !delta_weight, "rmsnorm: a norm of the delta without a delta");
+  MLL_REQUIRE(delta_eps >= 0.f, "rmsnorm: the delta's eps must be non-negative");
+  const mll::DeltaNorm dn{delta_weight, delta_eps, scale1, scale2};
   MLL_REQUIRE(width <= 50 * 1024, "rmsnorm: width %d exceeds the 51200 floats one block can hold", width);
   MLL_REQUIRE(eps >= 0.f, "rmsnorm: eps must be non-negative");
   MLL_REQUIRE(delta || !delta2, "rmsnorm: a second delta without a first");
   if (n_rows == 0) return 0;
   if (delta_dtype == MLL_F32 && out_dtype == MLL_F32)
-    return mll::launch_add_rmsnorm<float, float>(x, delta, delta2, weight, out, rows, n_rows, width, eps, stream);
+    return mll::launch_add_rmsnorm<float, float>(x, delta, delta2, weight, out, rows, n_rows, width, eps, dn, stream);
   if (delta_dtype == MLL_BF16 && out_dtype == MLL_BF16)
     return mll::launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(x, delta, delta2, weight, out, rows, n_rows,
-                                                                 width, eps, stream);
+                                                                 width, eps, dn, stream);
   if (delta_dtype == MLL_BF16 && out_dtype == MLL_F32)
     return mll::launch_add_rmsnorm<__nv_bfloat16, float>(x, delta, delta2, weight, out, rows, n_rows, width, eps,
-                                                         stream);
+                                                         dn, stream);
   MLL_REQUIRE(false, "rmsnorm: dtypes %d / %d", delta_dtype, out_dtype);
   return -1;
 }

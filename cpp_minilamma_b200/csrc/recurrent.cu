@@ -3,7 +3,8 @@
 //   S_t = diag(g_t) S_(t-1) + k_t u_t^T,      o_t = S_t^T q_t          S is [d, dv], float32
 //
 // with  u_t = v_t                              and one fixed decay per head      ("retention"), or
-//       u_t = beta_t (v_t - (diag(g_t) S_(t-1))^T k_t), g_t per key channel      (the gated delta rule).
+//       u_t = beta_t (v_t - (diag(g_t) S_(t-1))^T k_t), g_t per key channel      (the gated delta rule), or
+//       u_t = v_t                              and g_t per key channel           (gated linear attention).
 // The read-out sees the current token's write.  Everything that enters the recurrence is float32.
 //
 // Kernels (each for prompts and single tokens alike; a step's tokens of one sequence are consecutive rows):
@@ -12,6 +13,8 @@
 //   * delta_prepare       short causal convolution over time + silu on q, k, v (the inputs before this step's
 //                         first token come from the sequence's state), q and k to unit length per head,
 //                         q / sqrt(d), beta = sigmoid, g = exp(-exp(A) softplus(x + bias))
+//   * channel_decay_prepare  q * q_scale, k, v to float32 and g = sigmoid(z + bias)^(1 / tau) per key channel,
+//                         formed as exp(log_sigmoid(z + bias) / tau) in float32
 //   * conv_state_update   the last taps - 1 convolution inputs of every sequence, kept for the next step
 //   * state_scan          the recurrence: a column of S lives in the registers of R lanes (ROWS rows each);
 //                         per token every product is local to the column, two shuffles-reductions over the
@@ -146,6 +149,34 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepArgs a, int
   for (int e = lane; e < d; e += 32) dst[e] = conv_out[e] * f;
 }
 
+// grid (tokens), 256 threads: q * q_scale, k, v of a layer whose decay is sigmoid(z + bias)^(1 / tau) per key channel.
+struct ChannelDecayArgs {
+  const void* proj;    // [T, ld]: q (H * d), k (H * d), v (H * dv), then whatever else
+  const float* rate;   // [T, rate_ld]: z (H * d), float32
+  const float* bias;   // [H * d] or null
+  float* q;            // [T, H, d]
+  float* k;
+  float* v;            // [T, H, dv]
+  float* g;            // [T, H, d]
+  int ld, rate_ld, n_heads, d, dv;
+  float q_scale, inv_tau;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) channel_decay_prepare_kernel(ChannelDecayArgs a) {
+  const int t = blockIdx.x;
+  const int n = a.n_heads * a.d, nv = a.n_heads * a.dv;
+  const T* row = (const T*)a.proj + (size_t)t * a.ld;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    a.q[(size_t)t * n + i] = to_float(row[i]) * a.q_scale;
+    a.k[(size_t)t * n + i] = to_float(row[n + i]);
+    const float z = a.rate[(size_t)t * a.rate_ld + i] + (a.bias ? a.bias[i] : 0.f);
+    // log(sigmoid(z)) = -softplus(-z), without cancellation on either side
+    a.g[(size_t)t * n + i] = expf(-softplus_f(-z) * a.inv_tau);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) a.v[(size_t)t * nv + i] = to_float(row[2 * n + i]);
+}
+
 // grid (ceil(C / 128), sequences): new state = the last taps - 1 of (old state, this step's inputs)
 template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ conv_state,
@@ -192,8 +223,11 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 // are staged as 0, so their S stays 0 and adds nothing.  The tokens' q, k, g, v and beta arrive in shared memory
 // `tok_stage` tokens at a time through a two-stage ring of asynchronous copies, so that the next tokens load
 // while these are worked on and the chain from token to token is arithmetic only.
-template <int ROWS, int R, bool DELTA>
+// MODE 0: one decay per head; 1: the delta rule with a decay per key channel; 2: a decay per key channel, u = v.
+template <int ROWS, int R, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
+  constexpr bool DELTA = MODE == 1;    // beta and the correction by S^T k
+  constexpr bool CHANNEL = MODE != 0;  // g per key channel travels with q and k
   extern __shared__ __align__(16) float stage[];
   constexpr int DP = ROWS * R;          // padded number of rows
   constexpr int CPW = 32 / R;           // columns per warp
@@ -215,7 +249,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     s[i] = (live && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
   const int TS = a.tok_stage;
-  const int per_stage = (TS * DP * (DELTA ? 3 : 2) + TS * CPB + TS + 3) & ~3;  // stages start on 16-byte boundaries
+  const int per_stage = (TS * DP * (CHANNEL ? 3 : 2) + TS * CPB + TS + 3) & ~3;  // stages start on 16-byte boundaries
   // the padding rows of both stages, once: the copies below never touch them
   if (d < DP)
   for (int i = tid; i < 2 * TS * DP; i += SCAN_THREADS) {
@@ -224,7 +258,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
       float* base = stage + st * per_stage;
       base[rest] = 0.f;
       base[TS * DP + rest] = 0.f;
-      if (DELTA) base[2 * TS * DP + rest] = 1.f;
+      if (CHANNEL) base[2 * TS * DP + rest] = 1.f;
     }
   }
   auto load = [&](int t0, int st) {
@@ -232,7 +266,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     float* q_s = stage + st * per_stage;
     float* k_s = q_s + TS * DP;
     float* g_s = k_s + TS * DP;
-    float* v_s = stage + st * per_stage + TS * DP * (DELTA ? 3 : 2);
+    float* v_s = stage + st * per_stage + TS * DP * (CHANNEL ? 3 : 2);
     float* b_s = v_s + TS * CPB;
     if ((d & 3) == 0) {  // rows are whole 16-byte words
       const int words = d >> 2;
@@ -241,7 +275,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
         const size_t tok = (size_t)(row0 + t0 + tt);
         cp_async16(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
         cp_async16(k_s + tt * DP + e, a.k + (tok * G + kvh) * d + e);
-        if (DELTA) cp_async16(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
+        if (CHANNEL) cp_async16(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
       }
     } else {
       for (int i = tid; i < nt * d; i += SCAN_THREADS) {
@@ -249,7 +283,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
         const size_t tok = (size_t)(row0 + t0 + tt);
         cp_async4(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
         cp_async4(k_s + tt * DP + e, a.k + (tok * G + kvh) * d + e);
-        if (DELTA) cp_async4(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
+        if (CHANNEL) cp_async4(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
       }
     }
     for (int i = tid; i < nt * CPB; i += SCAN_THREADS) {
@@ -259,7 +293,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     if (DELTA)
       for (int i = tid; i < nt; i += SCAN_THREADS) cp_async4(b_s + i, a.beta + (size_t)(row0 + t0 + i) * H + h);
   };
-  const float decay = DELTA ? 1.f : a.head_decay[h];
+  const float decay = CHANNEL ? 1.f : a.head_decay[h];
   load(0, 0);
   cp_async_commit();
   for (int t0 = 0, it = 0; t0 < n_tok; t0 += TS, ++it) {
@@ -276,16 +310,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     const float* q_s = stage + st * per_stage;
     const float* k_s = q_s + TS * DP;
     const float* g_s = k_s + TS * DP;
-    const float* v_s = stage + st * per_stage + TS * DP * (DELTA ? 3 : 2);
+    const float* v_s = stage + st * per_stage + TS * DP * (CHANNEL ? 3 : 2);
     const float* b_s = v_s + TS * CPB;
     for (int tt = 0; tt < nt; ++tt) {
       // this lane's rows of q, k and g as 16-byte words (ROWS and DP are multiples of 4)
-      float qv[ROWS], kv[ROWS], gv[DELTA ? ROWS : 1];
+      float qv[ROWS], kv[ROWS], gv[CHANNEL ? ROWS : 1];
 #pragma unroll
       for (int i = 0; i < ROWS; i += 4) {
         *reinterpret_cast<float4*>(qv + i) = *reinterpret_cast<const float4*>(q_s + tt * DP + r * ROWS + i);
         *reinterpret_cast<float4*>(kv + i) = *reinterpret_cast<const float4*>(k_s + tt * DP + r * ROWS + i);
-        if (DELTA) *reinterpret_cast<float4*>(gv + i) = *reinterpret_cast<const float4*>(g_s + tt * DP + r * ROWS + i);
+        if (CHANNEL) *reinterpret_cast<float4*>(gv + i) = *reinterpret_cast<const float4*>(g_s + tt * DP + r * ROWS + i);
       }
       float u = live ? v_s[tt * CPB + warp * CPW + cw] : 0.f;
       if (DELTA) {
@@ -303,7 +337,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
       float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < ROWS; ++i) {
-        s[i] = DELTA ? fmaf(kv[i], u, s[i]) : fmaf(decay, s[i], kv[i] * u);
+        if (MODE == 1) s[i] = fmaf(kv[i], u, s[i]);
+        else if (MODE == 2) s[i] = fmaf(gv[i], s[i], kv[i] * u);
+        else s[i] = fmaf(decay, s[i], kv[i] * u);
         o4[i & 3] = fmaf(s[i], qv[i], o4[i & 3]);
       }
       float o_part = (o4[0] + o4[1]) + (o4[2] + o4[3]);
@@ -322,21 +358,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
   }
 }
 
-template <int ROWS, int R, bool DELTA>
+template <int ROWS, int R, int MODE>
 int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
   ScanArgs a = args;
   constexpr int DP = ROWS * R, CPB = (32 / R) * (SCAN_THREADS / 32);
   a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : (DP <= 512 ? 4 : 2));
-  const size_t smem = (size_t)2 * ((a.tok_stage * DP * (DELTA ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
+  const size_t smem = (size_t)2 * ((a.tok_stage * DP * (MODE ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
   const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
   if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) {
       mll_set_error("state scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
       return (int)err;
     }
   }
-  MLL_LAUNCH((state_scan_kernel<ROWS, R, DELTA>), grid, SCAN_THREADS, smem, stream, a);
+  MLL_LAUNCH((state_scan_kernel<ROWS, R, MODE>), grid, SCAN_THREADS, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -348,19 +384,19 @@ int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
 // rows a lane and four lanes a column, with twice the resident blocks, 142 us.  Otherwise (a prompt of one or a few
 // sequences) eight lanes share a column, so that eight times as many threads work on the chain from token
 // to token.
-template <bool DELTA>
+template <int MODE>
 int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
   const int d = a.d;
   const bool many = (long long)n_seqs * a.n_heads * a.dv >= (long long)mll_sm_count() * 512;
-  if (many && d <= 32) return launch_scan<32, 1, DELTA>(a, n_seqs, stream);
-  if (many && d <= 64) return launch_scan<64, 1, DELTA>(a, n_seqs, stream);
-  if (many && d <= 128) return launch_scan<64, 2, DELTA>(a, n_seqs, stream);
-  if (many && d <= 256) return launch_scan<64, 4, DELTA>(a, n_seqs, stream);
-  if (d <= 32) return launch_scan<4, 8, DELTA>(a, n_seqs, stream);
-  if (d <= 64) return launch_scan<8, 8, DELTA>(a, n_seqs, stream);
-  if (d <= 128) return launch_scan<16, 8, DELTA>(a, n_seqs, stream);
-  if (d <= 256) return launch_scan<32, 8, DELTA>(a, n_seqs, stream);
-  return launch_scan<32, 32, DELTA>(a, n_seqs, stream);
+  if (many && d <= 32) return launch_scan<32, 1, MODE>(a, n_seqs, stream);
+  if (many && d <= 64) return launch_scan<64, 1, MODE>(a, n_seqs, stream);
+  if (many && d <= 128) return launch_scan<64, 2, MODE>(a, n_seqs, stream);
+  if (many && d <= 256) return launch_scan<64, 4, MODE>(a, n_seqs, stream);
+  if (d <= 32) return launch_scan<4, 8, MODE>(a, n_seqs, stream);
+  if (d <= 64) return launch_scan<8, 8, MODE>(a, n_seqs, stream);
+  if (d <= 128) return launch_scan<16, 8, MODE>(a, n_seqs, stream);
+  if (d <= 256) return launch_scan<32, 8, MODE>(a, n_seqs, stream);
+  return launch_scan<32, 32, MODE>(a, n_seqs, stream);
 }
 
 // ---------------------------------------------------------------------------------------------- //
@@ -434,6 +470,24 @@ MLL_API int mll_delta_prepare(const void* proj, const float* rate, const float* 
   return 0;
 }
 
+MLL_API int mll_channel_decay_prepare(const void* proj, const float* rate, const float* bias, float* q, float* k, float* v,
+                                      float* g, int dtype, int n_tokens, int ld, int rate_ld, int n_heads, int d, int dv,
+                                      float q_scale, float tau, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && d > 0 && dv > 0, "channel decay prepare: bad sizes");
+  MLL_REQUIRE(ld >= n_heads * (2 * d + dv) && rate_ld >= n_heads * d, "channel decay prepare: row strides %d / %d too short", ld, rate_ld);
+  MLL_REQUIRE(tau > 0.f, "channel decay prepare: tau must be positive");
+  if (n_tokens == 0) return 0;
+  mll::ChannelDecayArgs a{proj, rate, bias, q, k, v, g, ld, rate_ld, n_heads, d, dv, q_scale, 1.f / tau};
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::channel_decay_prepare_kernel<float>), n_tokens, 256, 0, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::channel_decay_prepare_kernel<__nv_bfloat16>), n_tokens, 256, 0, stream, a);
+  else
+    MLL_REQUIRE(false, "channel decay prepare: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
 MLL_API int mll_conv_state_update(const void* proj, int dtype, int ld, float* conv_state, const int* seq_slot,
                                   const int* seq_qstart, const int* seq_qlen, int n_seqs, int channels, int taps,
                                   cudaStream_t stream) {
@@ -453,18 +507,23 @@ MLL_API int mll_conv_state_update(const void* proj, int dtype, int ld, float* co
   return 0;
 }
 
-// delta != 0: the gated delta rule (g, beta given); else one decay per head (head_decay given).
+// mode 1: the gated delta rule (g, beta given); 2: a decay per key channel without the delta rule (g given);
+// 0: one decay per head (head_decay given).
 MLL_API int mll_state_scan(const float* q, const float* k, const float* v, const float* g, const float* beta,
                            const float* head_decay, float* state, float* out, const int* seq_slot,
                            const int* seq_qstart, const int* seq_qlen, int n_seqs, int n_heads, int n_kv_heads, int d,
-                           int dv, int delta, cudaStream_t stream) {
+                           int dv, int mode, cudaStream_t stream) {
   MLL_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "state scan: bad head counts");
   MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0, "state scan: head sizes %d / %d (keys at most 1024)", d, dv);
   MLL_REQUIRE(n_heads <= 65535 && n_seqs <= 65535, "state scan: too many heads or sequences for one launch");
-  MLL_REQUIRE(delta ? (g && beta) : (head_decay != nullptr), "state scan: the decay's inputs are missing");
+  MLL_REQUIRE(mode >= 0 && mode <= 2, "state scan: unknown mode %d", mode);
+  MLL_REQUIRE(mode == 1 ? (g && beta) : (mode == 2 ? g != nullptr : head_decay != nullptr),
+              "state scan: the decay's inputs are missing");
   if (n_seqs == 0) return 0;
   mll::ScanArgs a{q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, seq_qlen, n_heads, n_kv_heads, d, dv, 0};
-  return delta ? mll::dispatch_scan<true>(a, n_seqs, stream) : mll::dispatch_scan<false>(a, n_seqs, stream);
+  if (mode == 1) return mll::dispatch_scan<1>(a, n_seqs, stream);
+  if (mode == 2) return mll::dispatch_scan<2>(a, n_seqs, stream);
+  return mll::dispatch_scan<0>(a, n_seqs, stream);
 }
 
 MLL_API int mll_head_norm_gate(const float* o, const float* weight, const void* gate, int gate_dtype, int gate_ld,

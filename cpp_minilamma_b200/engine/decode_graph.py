@@ -76,7 +76,7 @@ class _Captured:
             max_ctx=engine.model.max_positions, small_rows=engine.small_rows, shape=shape)
         for key, _, name, offset, count in self.meta_layout:
             self.state.meta.setdefault(key, {})[name] = self.dev[offset:offset + count]
-        for part in engine.model.all_parts():
+        for part in engine.model.leaf_parts():
             fixed = part.capture_parameters(batch, engine.model.max_positions)
             if fixed:
                 self.state.fixed[part] = fixed

@@ -11,7 +11,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import (Block, BuildContext, CacheNeed, FeedForward, Mixer, ModelSpec, Norm, WeightSpec,
+from ..parts.base import (EMBEDDING_ENTRY, Block, BuildContext, CacheNeed, FeedForward, Mixer, ModelSpec, Norm, WeightSpec,
                           WeightStore, build_part)
 
 
@@ -70,6 +70,19 @@ class Model:
         parts.extend([self.final_norm, self.lm_head])
         return parts
 
+    def leaf_parts(self):
+        """`all_parts` with every part that is made of others (`sub_parts`) followed by those."""
+        out = []
+
+        def walk(part):
+            out.append(part)
+            for inner in getattr(part, "sub_parts", lambda: [])():
+                walk(inner)
+
+        for part in self.all_parts():
+            walk(part)
+        return out
+
     def weight_specs(self) -> List[WeightSpec]:
         specs: List[WeightSpec] = []
         seen = set()
@@ -113,8 +126,12 @@ class Model:
 
     # ---- cache needs ---------------------------------------------------------- #
     def cache_needs(self) -> List[Tuple[int, Optional[int], CacheNeed]]:
-        return [(i, entry.cache_of, self.layers[entry.layer].mixer.cache_need())
-                for i, entry in enumerate(self.spec.schedule)]
+        needs = [(i, entry.cache_of, self.layers[entry.layer].mixer.cache_need())
+                 for i, entry in enumerate(self.spec.schedule)]
+        own = self.embedding.cache_need()
+        if own is not None:  # an embedding that carries something from token to token
+            needs.append((EMBEDDING_ENTRY, None, own))
+        return needs
 
     # ---- forward ---------------------------------------------------------------- #
     def forward(self, step, cache, tokens: torch.Tensor, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -122,7 +139,10 @@ class Model:
         [n_want, vocab] of the rows in `want_rows` (int32), or None when nothing is wanted."""
         if not self.bound:
             raise RuntimeError("the model has no weights bound")
-        x = self.embedding.forward(step, tokens)
+        if self.embedding.cache_need() is not None:
+            x = self.embedding.forward(step, tokens, cache.view(EMBEDDING_ENTRY))
+        else:
+            x = self.embedding.forward(step, tokens)
         pending = None
         schedule = self.spec.schedule
         x0 = None

@@ -209,7 +209,7 @@ class Engine:
         self.ws = Workspace(self.device)
         self.max_step_tokens = max(int(max_step_tokens), PAGE)
         self.vocab_size = model.spec.vocab_size
-        self.providers = metadata_providers(model.all_parts())
+        self.providers = metadata_providers(model.leaf_parts())
         self._meta_host: Optional[torch.Tensor] = None
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_copied = None

@@ -5,5 +5,5 @@ from .base import (Block, BuildContext, CacheNeed, FeedForward, KVNeed, LayerSpe
                    PartSpec, PendingSum, PositionEncoding, ScheduleEntry, StateNeed, StreamOp, WeightSpec, WeightStore, build_part,
                    known_parts, register_part)
 from . import (attention, block, chunked_attention, embedding, latent_attention, mlp, moe, norm, reentry, rope,  # noqa: F401
-               state_mixers)  # (registration)
+               side_by_side, state_mixers)  # (registration)
 from .linear import Linear

@@ -111,10 +111,10 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Fixed-size state per sequence: named tensors of the given shapes, float32, zeroed
-    when a slot is handed out."""
+    """Fixed-size state per sequence: named tensors of the given shapes, zeroed when a slot is handed out.
+    An entry is (name, shape) for float32 or (name, shape, "int32") for integers (a token id, a counter)."""
 
-    tensors: Tuple[Tuple[str, Tuple[int, ...]], ...]
+    tensors: Tuple[Tuple, ...]
 
 
 @dataclass(frozen=True)
@@ -155,10 +155,23 @@ class ResidualTarget:
 class PendingSum:
     """The outputs of two parts that read the same norm (a block whose mixer and feed-forward run side by
     side), both still to be added to the residual stream: the next norm adds `first + second` to it in
-    float32 in the same kernel that normalises."""
+    float32 in the same kernel that normalises.  `scale_first`, `scale_second`: factors on the two (a mixer made of
+    two mixers side by side, each with a weight of its own)."""
 
     first: torch.Tensor
     second: torch.Tensor
+    scale_first: float = 1.0
+    scale_second: float = 1.0
+
+
+@dataclass
+class NormedDelta:
+    """A part's output (a tensor or a `PendingSum`) that passes a norm of its own on its way into the residual
+    stream:  x += norm(delta).  The next norm that reads the stream does both in its one kernel (a norm without an
+    RMS form cannot; it refuses)."""
+
+    delta: Any
+    norm: "Norm"
 
 
 # --------------------------------------------------------------------------- #
@@ -302,6 +315,9 @@ class StreamOp(Part):
         """Rewrite the float32 stream `x` [T, D] in place.  `pending` is the output of the part before, still
         to be added to x first (a tensor or None); `x0` is the stream as the embedding left it."""
         raise NotImplementedError
+
+
+EMBEDDING_ENTRY = -1  # the key of the embedding's per-sequence state among the cache's entries (layers count from 0)
 
 
 class Mixer(Part):

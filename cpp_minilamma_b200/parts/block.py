@@ -4,6 +4,8 @@
     r = x + mixer(norm_in(x));   x' = r + feed_forward(norm_post(r))
 `parallel` (not in the reference) lets mixer and feed-forward read one norm:
     h = norm(x);   x' = x + mixer(h) + feed_forward(h)
+`sandwich` (not in the reference) puts a norm behind each sub-layer as well as in front of it:
+    r = x + norm_mo(mixer(norm_in(x)));   x' = r + norm_fo(feed_forward(norm_pf(r)))
 The residual adds are not separate kernels: a part's output stays "pending" until the
 next norm, which adds it to the float32 residual and normalises in one pass.  Where the parts on both
 sides of a norm offer it, the norm is no kernel either: the part before adds to the residual stream
@@ -13,7 +15,8 @@ from __future__ import annotations
 
 from typing import List
 
-from .base import Block, PendingSum, ResidualTarget, register_part
+from .mlp import NoFeedForward
+from .base import Block, NormedDelta, PendingSum, ResidualTarget, register_part
 
 
 def _offer(x, norm, writer, reader):
@@ -59,5 +62,26 @@ class ParallelBlock(Block):
         return mixed if fed is None else PendingSum(mixed, fed)
 
 
+class SandwichBlock(Block):
+    """Norms "input" and "mixer_out" around the mixer, "pre_ff" and "ff_out" around the feed-forward.  A sub-layer's
+    output stays pending together with the norm behind it (`NormedDelta`): the norm that reads the stream next
+    normalises the output, adds it and normalises the sum in one kernel.  A layer without a feed-forward ends behind
+    "mixer_out"."""
+
+    capturable = True
+
+    def norm_names(self) -> List[str]:
+        return ["input", "mixer_out", "pre_ff", "ff_out"]
+
+    def forward(self, step, x, pending, layer, cache):
+        h = layer.norms["input"].forward(step, x, pending)
+        mixed = NormedDelta(layer.mixer.forward(step, h, cache), layer.norms["mixer_out"])
+        if isinstance(layer.feed_forward, NoFeedForward):
+            return mixed
+        h = layer.norms["pre_ff"].forward(step, x, mixed)
+        return NormedDelta(layer.feed_forward.forward(step, h), layer.norms["ff_out"])
+
+
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "parallel", ParallelBlock)

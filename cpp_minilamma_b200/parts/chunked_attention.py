@@ -9,7 +9,8 @@
 
 Options beyond that, each a parameter: a query temperature (q at position p times 1 + coef * ln(floor((p + 1) /
 every) + 1)); a sink in the softmax (weights exp(s_j) / (1 + sum_j exp(s_j)): one more key that scores 0 and carries
-no value); an output gate read from the mixer's own input, one number per head (head h's output times
+no value), or a learned one (exp(c_h) in place of the 1, c_h a number per query head that no scale touches); values
+that are the keys themselves as projected, before norm and rotation (no W_v; dv == d); an output gate read from the mixer's own input, one number per head (head h's output times
 sigmoid(W_g h)_h) or one per element, applied before W_o.
 
 Chunks count from position 0 of the sequence, not from where a step's tokens begin.  Keys and values live in
@@ -40,7 +41,11 @@ class ChunkedAttention(Mixer):
       rotary_dims                                   how many leading dimensions of a head are rotated
       qk_norm                                       None or {"q": tensor name, "k": tensor name, "eps": float}
       q_temp                                        None or {"coef": float, "every": int}: the query temperature
-      sink                                          True: the softmax's denominator has one more term exp(0)
+      sink                                          True: the softmax's denominator has one more term exp(0); a tensor
+                                                    name: one more term exp(c_h), c [n_heads] loaded under that name
+      values                                        "projected" (default) or "keys": v = W_k h, no names["v"]
+      out_name                                      workspace name of the result (default "o"; two mixers whose results
+                                                    are both pending need two)
       gate                                          None, "head" or "element": an output gate sigmoid(W_g h), names["g"]
       names                                         {"q","k","v","o"} (and "g"): tensor names
     """
@@ -60,7 +65,16 @@ class ChunkedAttention(Mixer):
         self.qk_norm = dict(params["qk_norm"]) if params.get("qk_norm") else None
         q_temp = params.get("q_temp")
         self.q_temp = (float(q_temp["coef"]), int(q_temp["every"])) if q_temp else None
-        self.sink = bool(params.get("sink", False))
+        sink = params.get("sink", False)
+        self.sink_name = sink if isinstance(sink, str) else None
+        self.sink = bool(sink)
+        self.sink_values: Optional[torch.Tensor] = None
+        self.v_from_k = (params.get("values") or "projected") == "keys"
+        if params.get("values") not in (None, "projected", "keys"):
+            raise ValueError(f"attention: values {params.get('values')!r} are neither 'projected' nor 'keys'")
+        if self.v_from_k and self.dv != self.d:
+            raise ValueError(f"attention: values that are the keys have their size, got {self.dv} / {self.d}")
+        self.out_name = params.get("out_name") or "o"
         self.gate = params.get("gate") or None
         if self.gate not in (None, "head", "element"):
             raise ValueError(f"attention: gate {self.gate!r} is neither 'head' nor 'element'")
@@ -82,8 +96,11 @@ class ChunkedAttention(Mixer):
         D = self.ctx.hidden_size
         specs = [WeightSpec(self.names["q"], (self.n_heads * self.d, D)),
                  WeightSpec(self.names["k"], (self.n_kv_heads * self.d, D)),
-                 WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)),
                  WeightSpec(self.names["o"], (D, self.n_heads * self.dv))]
+        if not self.v_from_k:
+            specs.insert(2, WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)))
+        if self.sink_name:
+            specs.append(WeightSpec(self.sink_name, (self.n_heads,), kind="vector", init="normal"))
         if self.gate:
             specs.append(WeightSpec(self.names["g"], (self._gate_width(), D)))
         if self.qk_norm:
@@ -96,11 +113,18 @@ class ChunkedAttention(Mixer):
 
     def bind(self, store) -> None:
         # the gate reads the same rows as q, k and v: its matrix rides behind theirs in the one fused product
-        mats = [store.take(self.names[p]) for p in (("q", "k", "v", "g") if self.gate else ("q", "k", "v"))]
+        parts = [p for p in ("q", "k", "v", "g") if (p != "v" or not self.v_from_k) and (p != "g" or self.gate)]
+        mats = [store.take(self.names[p]) for p in parts]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
-        self.qkv = Linear(torch.cat(mats, dim=0), self.names["q"] + "+k+v" + ("+g" if self.gate else ""))
-        del mats
+        fused = torch.cat(mats, dim=0)
+        spare = -fused.shape[0] % 8  # rows of zeros up to a multiple of 8: the product's rows stay 16-byte aligned
+        if spare:
+            fused = torch.cat([fused, torch.zeros((spare, fused.shape[1]), dtype=fused.dtype, device=fused.device)], dim=0)
+        self.qkv = Linear(fused, "+".join(self.names[p] if p == "q" else p for p in parts))
+        del mats, fused
+        if self.sink_name:
+            self.sink_values = store.take(self.sink_name)
         self.o = Linear(store.take(self.names["o"]), self.names["o"])
         if self.qk_norm:
             self.q_weight = store.take(self.qk_norm["q"])
@@ -152,18 +176,20 @@ class ChunkedAttention(Mixer):
                                   step.seq_slot, cache.block_table, q, cache.k, cache.v, self.n_heads,
                                   self.n_kv_heads, self.d, self.dv, self.rot,
                                   bool(self.position.interleaved) if self.position is not None else False,
-                                  float(self.qk_norm["eps"]) if self.qk_norm else 0.0, q_temp=self.q_temp)
+                                  float(self.qk_norm["eps"]) if self.qk_norm else 0.0, q_temp=self.q_temp,
+                                  v_from_k=self.v_from_k)
         out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
         self._attend(step, q, cache, out)
         if self.gate:
-            K.heads_gate(out, qkv, self.n_heads * self.d + self.n_kv_heads * (self.d + self.dv), out, self.n_heads,
-                         self.dv, per_head=self.gate == "head")
-        return self.o.forward(step, out, "o")
+            gate_col = self.n_heads * self.d + self.n_kv_heads * (self.d if self.v_from_k else self.d + self.dv)
+            K.heads_gate(out, qkv, gate_col, out, self.n_heads, self.dv, per_head=self.gate == "head")
+        return self.o.forward(step, out, self.out_name)
 
     def _attend(self, step, q, cache, out) -> None:
         act = self.ctx.act_dtype
+        learned = self.sink_values  # a sink with a score of its own: the kernels of this file's own family take it
         if (step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
-                and not (self.chunk and self.window) and act == torch.bfloat16
+                and not (self.chunk and self.window) and act == torch.bfloat16 and learned is None
                 and (not self.sink or K.USE_TENSOR_CORE_DECODE)):
             # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
             # mma.sync), which take the chunk as the key range's start; one block per (sequence, kv head)
@@ -180,10 +206,11 @@ class ChunkedAttention(Mixer):
                                      torch.float32) if splits > 1 else None
             K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     cache.block_table, out, step.n_seqs, self.n_heads, self.n_kv_heads, self.d, self.dv,
-                                    self.chunk, self.window, self.scale, sink=self.sink, n_splits=splits, scratch=scratch)
+                                    self.chunk, self.window, self.scale, sink=self.sink, n_splits=splits, scratch=scratch,
+                                    sink_values=learned)
             return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+        if tiles and self.d == self.dv and learned is None and K.attention_prefill_takes_chunks(act, self.d):
             # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
             # which knows the chunk mask too
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
@@ -196,11 +223,11 @@ class ChunkedAttention(Mixer):
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out, self.n_heads,
                                     self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
-                                    sink=self.sink)
+                                    sink=self.sink, sink_values=learned)
             return
         K.local_attention(q, cache.k, cache.v, step.tok_pos, step.tok_seq, step.seq_slot, cache.block_table, out,
                           self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
-                          sink=self.sink)
+                          sink=self.sink, sink_values=learned)
 
 
 register_part("mixer", "chunked_attention", ChunkedAttention)

@@ -12,7 +12,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, Part, WeightSpec, build_part, register_part
+from .base import BuildContext, CacheNeed, Part, StateNeed, WeightSpec, build_part, register_part
 from .linear import Linear
 
 
@@ -40,9 +40,61 @@ class TokenEmbedding(Part):
         if self.norm is not None:
             self.norm.bind(store)
 
+    def cache_need(self):
+        """None: nothing is carried from token to token."""
+        return None
+
     def forward(self, step, tokens: torch.Tensor) -> torch.Tensor:
         x = step.ws.buffer("x", (tokens.shape[0], self.ctx.hidden_size), torch.float32)
         K.embedding(tokens, self.table, x)
+        if self.norm is not None:
+            self.norm.forward_in_place(x)
+        return x
+
+
+class PairHashEmbedding(TokenEmbedding):
+    """x = scale * E[token] + B[(mul_prev * previous token + mul_cur * token) mod buckets], and B's last row
+    (row `buckets`) for a sequence's first token.  The token before a step's first one is per-sequence state, kept
+    in the cache beside the mixers' (one int32 per slot), so a prompt may arrive in portions and decoding goes on
+    from where the prompt ended.
+
+    params: vocab, name, scale (default 1), pairs: None or {"name", "buckets", "mul_prev", "mul_cur"}."""
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.scale = float(params.get("scale", 1.0))
+        pairs = params.get("pairs") or None
+        self.pairs_name = pairs["name"] if pairs else None
+        self.buckets = int(pairs["buckets"]) if pairs else 0
+        self.mul_prev = int(pairs["mul_prev"]) if pairs else 0
+        self.mul_cur = int(pairs["mul_cur"]) if pairs else 0
+        if pairs and self.buckets < 1:
+            raise ValueError(f"pair embedding: {self.buckets} buckets")
+        self.pairs: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = super().weight_specs()
+        if self.pairs_name:
+            specs.append(WeightSpec(self.pairs_name, (self.buckets + 1, self.ctx.hidden_size)))
+        return specs
+
+    def bind(self, store) -> None:
+        super().bind(store)
+        if self.pairs_name:
+            self.pairs = store.take(self.pairs_name)
+            if self.pairs.dtype != self.table.dtype:  # one of the two stored in 32-bit: both are read as 32-bit
+                self.pairs, self.table = self.pairs.float(), self.table.float()
+
+    def cache_need(self):
+        return CacheNeed(state=StateNeed((("previous", (), "int32"),)))
+
+    def forward(self, step, tokens: torch.Tensor, cache=None) -> torch.Tensor:
+        if cache is None:
+            raise RuntimeError("pair embedding: the step came without the embedding's state")
+        x = step.ws.buffer("x", (tokens.shape[0], self.ctx.hidden_size), torch.float32)
+        K.embedding_pair(tokens, step.tok_pos, step.tok_seq, step.seq_slot, step.seq_qstart, step.seq_qlen,
+                         cache.state["previous"], self.table, self.pairs, x, self.buckets, self.mul_prev, self.mul_cur,
+                         self.scale)
         if self.norm is not None:
             self.norm.forward_in_place(x)
         return x
@@ -79,4 +131,5 @@ class LMHead(Part):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("lm_head", "linear_head", LMHead)

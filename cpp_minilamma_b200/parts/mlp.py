@@ -88,6 +88,43 @@ class SwiGLUFeedForward(FeedForward):
         return self.down.forward(step, act, "down", into=into)
 
 
+class GeluFeedForward(FeedForward):
+    """down(act(up(h))) without a gate: act is gelu in its erf form, 0.5 z (1 + erf(z / sqrt 2)), or in its tanh form.
+    params: intermediate, names {"up","down"} (tensor names), activation ("gelu_erf" default, or "gelu_tanh"),
+    out_name (workspace name of the result, default "down")."""
+
+    capturable = True
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.inter = int(params["intermediate"])
+        self.names = dict(params["names"])
+        kinds = {"gelu_erf": K.ACT_GELU_ERF, "gelu_tanh": K.ACT_GELU_TANH}
+        name = params.get("activation") or "gelu_erf"
+        if name not in kinds:
+            raise ValueError(f"feed-forward: activation {name!r} is not one of {sorted(kinds)}")
+        self.act = kinds[name]
+        self.out_name = params.get("out_name") or "down"
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D = self.ctx.hidden_size
+        return [WeightSpec(self.names["up"], (self.inter, D)), WeightSpec(self.names["down"], (D, self.inter))]
+
+    def bind(self, store) -> None:
+        self.up = Linear(store.take(self.names["up"]), self.names["up"])
+        self.down = Linear(store.take(self.names["down"]), self.names["down"])
+
+    def parameter_bytes(self) -> int:
+        return self.up.parameter_bytes() + self.down.parameter_bytes()
+
+    def forward(self, step, h, into=None):
+        u = self.up.forward(step, h, "up")
+        K.activation(u, u, self.act)
+        return self.down.forward(step, u, self.out_name)
+
+
 class NoFeedForward(FeedForward):
     """A layer without a feed-forward: contributes nothing (blocks that add two outputs skip a None)."""
 
@@ -98,4 +135,5 @@ class NoFeedForward(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+register_part("feed_forward", "gelu_mlp", GeluFeedForward)
 register_part("feed_forward", "none", NoFeedForward)

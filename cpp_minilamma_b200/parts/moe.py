@@ -5,6 +5,12 @@
     weights = softmax over the chosen logits alone
     out     = sum_j weights_j * expert_{chosen_j}(h)  +  shared(h)        expert(h) = W_down (silu(W_gate h) * W_up h)
 
+Other forms, each a parameter: scores over all experts (s = softmax(z) over every expert; the choice goes by s + a
+stored correction, the weights are the chosen s over their sum, times a constant); experts without a gate,
+W_down gelu(W_up h); identity experts - the router's last rows belong to experts without tensors, whose output is
+their input times the weight; a gate on the shared expert, sigmoid(w_g . h), one number per token, whose row rides
+behind the router's so that the routing kernel forms it.
+
 The experts' matrices are stacked ([E, 2 I, D] gate rows then up rows, and [E, D, I]); the routing stays on the
 device: the (token, choice) pairs are sorted by expert there and the two products run over tiles of one expert's
 rows (csrc/moe.cu), so a step's launches follow from its number of tokens alone and decode steps replay from a
@@ -28,7 +34,14 @@ class RoutedFeedForward(FeedForward):
       router_bias                     True: the router has a bias
       names                           {"router", "router_bias", "expert": a pattern with {e} and {p}} where p is one of
                                       gate, up, down
-      shared                          None, or the params of a `swiglu` part that every token also goes through
+      shared                          None, or the params of a feed-forward part that every token also goes through
+      shared_kind                     that part's kind ("swiglu" by default)
+      shared_gate                     None, or the tensor name of a [1, D] matrix: the shared output times sigmoid(w . h)
+      scoring                         "chosen" (softmax over the chosen logits, the default) or "all" (see above;
+                                      names["correction"] is then the correction, `scale` the constant)
+      identity                        experts behind the `experts` real ones that hand their input on (router rows
+                                      experts .. experts + identity - 1)
+      expert_form                     "swiglu" (default) or "gelu" (names' p is then one of up, down)
     """
 
     capturable = True
@@ -41,10 +54,24 @@ class RoutedFeedForward(FeedForward):
         self.inter = int(params["intermediate"])
         self.names = dict(params["names"])
         self.has_bias = bool(params.get("router_bias", False))
-        if not 1 <= self.top <= min(self.experts, 32):
-            raise ValueError(f"routed feed-forward: top {self.top} of {self.experts} experts (at most 32)")
-        self.shared = build_part("feed_forward", PartSpec("swiglu", dict(params["shared"])), ctx) \
+        self.identity = int(params.get("identity") or 0)
+        self.routed = self.experts + self.identity  # rows of the router
+        self.all_scores = (params.get("scoring") or "chosen") == "all"
+        if params.get("scoring") not in (None, "chosen", "all"):
+            raise ValueError(f"routed feed-forward: scoring {params.get('scoring')!r} is neither 'chosen' nor 'all'")
+        self.scale = float(params.get("scale", 1.0))
+        self.gelu = (params.get("expert_form") or "swiglu") == "gelu"
+        if params.get("expert_form") not in (None, "swiglu", "gelu"):
+            raise ValueError(f"routed feed-forward: expert form {params.get('expert_form')!r}")
+        if self.all_scores and self.has_bias:
+            raise ValueError("routed feed-forward: scores over all experts take a correction, not a router bias")
+        if not self.all_scores and (self.scale != 1.0 or self.identity):
+            raise ValueError("routed feed-forward: a weight scale or identity experts need scoring 'all'")
+        if not 1 <= self.top <= min(self.routed, 32):
+            raise ValueError(f"routed feed-forward: top {self.top} of {self.routed} experts (at most 32)")
+        self.shared = build_part("feed_forward", PartSpec(params.get("shared_kind") or "swiglu", dict(params["shared"])), ctx) \
             if params.get("shared") else None
+        self.shared_gate_name = params.get("shared_gate") if self.shared is not None else None
         self.router: Optional[torch.Tensor] = None
         self.router_bias: Optional[torch.Tensor] = None
         self.gate_up: Optional[torch.Tensor] = None
@@ -55,21 +82,34 @@ class RoutedFeedForward(FeedForward):
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.ctx.hidden_size
-        specs = [WeightSpec(self.names["router"], (self.experts, D), kind="vector", init="normal")]
+        specs = [WeightSpec(self.names["router"], (self.routed, D), kind="vector", init="normal")]
         if self.has_bias:
             specs.append(WeightSpec(self.names["router_bias"], (self.experts,), kind="vector", init="normal"))
+        if self.all_scores and self.names.get("correction"):
+            specs.append(WeightSpec(self.names["correction"], (self.routed,), kind="vector", init="normal"))
         for e in range(self.experts):
-            specs += [WeightSpec(self._expert(e, "gate"), (self.inter, D)), WeightSpec(self._expert(e, "up"), (self.inter, D)),
-                      WeightSpec(self._expert(e, "down"), (D, self.inter))]
+            if not self.gelu:
+                specs.append(WeightSpec(self._expert(e, "gate"), (self.inter, D)))
+            specs += [WeightSpec(self._expert(e, "up"), (self.inter, D)), WeightSpec(self._expert(e, "down"), (D, self.inter))]
+        if self.shared_gate_name:
+            specs.append(WeightSpec(self.shared_gate_name, (1, D), kind="vector", init="normal"))
         return specs + (self.shared.weight_specs() if self.shared is not None else [])
+
+    def sub_parts(self):
+        return [self.shared] if self.shared is not None else []
 
     def bind(self, store) -> None:
         self.router = store.take(self.names["router"])  # float32: the logits are 32-bit whatever the run's dtype
+        if self.shared_gate_name:  # the shared expert's gate: one more row behind the experts'
+            self.router = torch.cat([self.router, store.take(self.shared_gate_name).float()], dim=0).contiguous()
         self.router_bias = store.take(self.names["router_bias"]) if self.has_bias else None
+        if self.all_scores and self.names.get("correction"):
+            self.router_bias = store.take(self.names["correction"])  # corrects the choice, not the logits
         act = self.ctx.act_dtype
         gate_up, down = [], []
         for e in range(self.experts):
-            gate_up.append(torch.cat([store.take(self._expert(e, "gate")).to(act), store.take(self._expert(e, "up")).to(act)]))
+            up = store.take(self._expert(e, "up")).to(act)
+            gate_up.append(up if self.gelu else torch.cat([store.take(self._expert(e, "gate")).to(act), up]))
             down.append(store.take(self._expert(e, "down")).to(act))
         self.gate_up = torch.stack(gate_up).contiguous()
         self.down = torch.stack(down).contiguous()
@@ -85,10 +125,10 @@ class RoutedFeedForward(FeedForward):
                 + (self.shared.parameter_bytes() if self.shared is not None else 0))
 
     def _plan(self, step, n_pairs: int, mma: bool) -> K.MoePlan:
-        rows = K.moe_tile_rows(mma, n_pairs, self.experts)
-        tiles = K.moe_max_tiles(n_pairs, self.experts, rows)
+        rows = K.moe_tile_rows(mma, n_pairs, self.routed)
+        tiles = K.moe_max_tiles(n_pairs, self.routed, rows)
         ws = step.ws
-        return K.MoePlan(ws.buffer("moe.order", (n_pairs,), torch.int32), ws.buffer("moe.offsets", (self.experts + 1,), torch.int32),
+        return K.MoePlan(ws.buffer("moe.order", (n_pairs,), torch.int32), ws.buffer("moe.offsets", (self.routed + 1,), torch.int32),
                          ws.buffer("moe.tile_expert", (tiles,), torch.int32), ws.buffer("moe.tile_row0", (tiles,), torch.int32),
                          ws.buffer("moe.n_tiles", (1,), torch.int32), rows, mma)
 
@@ -108,21 +148,28 @@ class RoutedFeedForward(FeedForward):
             if h.dtype != torch.float32:
                 wide = ws.buffer("moe.h32", (T, D), torch.float32)
                 K.cast(h, wide)
-            logits = ws.buffer("moe.logits", (T, self.experts), torch.float32)
+            logits = ws.buffer("moe.logits", (T, self.router.shape[0]), torch.float32)
             torch.mm(wide, self.router.t(), out=logits)
-        K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top, logits=logits)
+        shared_gate = ws.buffer("moe.shared_gate", (T,), torch.float32) if self.shared_gate_name else None
+        K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top, logits=logits, all_scores=self.all_scores,
+                    scale=self.scale, gate_out=shared_gate)
         # bfloat16: tiles of 64 rows on tensor cores at every size - with few rows per expert the products stream each
         # touched expert's weights once, and a mostly empty tile costs nothing that memory does not hide
         mma = K.USE_TENSOR_CORE_MOE and K.moe_mma_supported(act, D, self.inter)
         plan = self._plan(step, n_pairs, mma)
-        K.moe_sort(chosen, plan, self.experts)
+        K.moe_sort(chosen, plan, self.routed, n_real=self.experts)
         hidden = ws.buffer("moe.act", (n_pairs, self.inter), act)
-        K.moe_gate_up(h, self.gate_up, hidden, plan, self.top)
+        K.moe_gate_up(h, self.gate_up, hidden, plan, self.top, form=K.EXPERT_GELU if self.gelu else K.EXPERT_SWIGLU,
+                      n_experts=self.routed)
         y = ws.buffer("moe.y", (n_pairs, D), torch.float32)
-        K.moe_down(hidden, self.down, y, weight, plan, self.top)
+        K.moe_down(hidden, self.down, y, weight, plan, self.top, n_experts=self.routed)
         shared = self.shared.forward(step, h) if self.shared is not None else None
         out = ws.buffer("moe.out", (T, D), act)
-        K.moe_combine(y, shared, out, self.top)
+        if self.identity:
+            K.moe_combine(y, shared, out, self.top, chosen=chosen, pair_weight=weight, h=h, n_real=self.experts,
+                          other_gate=shared_gate)
+        else:
+            K.moe_combine(y, shared, out, self.top, other_gate=shared_gate)
         return out
 
 

@@ -12,6 +12,11 @@ f is kept when lam < L0 / high_freq_factor, divided by `factor` when
 lam > L0 / low_freq_factor, and otherwise blended with
 s = (L0 / lam - low) / (high - low):  f' = (1 - s) f / factor + s f.
 
+`scaling` of type "yarn" (not in the reference) blends by pair index instead: with
+pair(t) = d ln(L0 / (2 pi t)) / (2 ln theta) - the pair whose wavelength makes t turns over the original length L0 -
+lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), d - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
+f'_i = ramp_i f_i / factor + (1 - ramp_i) f_i, and cos and sin are both multiplied by 0.1 ln(factor) + 1.
+
 `interleaved` selects the pairing: True pairs (2i, 2i+1) (the reference's Normal type),
 False pairs (i, i + d/2) (its NeoX type), src/ops.cc:206-210.
 """
@@ -31,6 +36,16 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Dict[str,
     freqs = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / head_dim)
     if not scaling:
         return freqs
+    if scaling.get("type") == "yarn":
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def pair_of(turns: float) -> float:
+            return head_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+        lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["slow"]))), head_dim - 1)
+        ramp = np.clip((np.arange(half, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return freqs / factor * ramp + freqs * (1.0 - ramp)
     factor = float(scaling["factor"])
     low = float(scaling["low_freq_factor"])
     high = float(scaling["high_freq_factor"])
@@ -40,6 +55,13 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Dict[str,
     blended = (1.0 - smooth) * freqs / factor + smooth * freqs
     return np.where(wavelength < original / high, freqs,
                     np.where(wavelength > original / low, freqs / factor, blended))
+
+
+def table_magnitude(scaling: Optional[Dict[str, Any]]) -> float:
+    """The factor on every cos and sin: 0.1 ln(factor) + 1 under "yarn" scaling, else 1."""
+    if scaling and scaling.get("type") == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 class RotaryEncoding(PositionEncoding):
@@ -53,8 +75,9 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary encoding needs an even head_dim, got {self.head_dim}")
         freqs = inverse_frequencies(self.head_dim, float(params["theta"]), params.get("scaling"))
         angles = np.arange(ctx.max_positions, dtype=np.float64)[:, None] * freqs[None, :]
-        self.cos = torch.from_numpy(np.cos(angles).astype(np.float32)).to(ctx.device)
-        self.sin = torch.from_numpy(np.sin(angles).astype(np.float32)).to(ctx.device)
+        magnitude = table_magnitude(params.get("scaling"))
+        self.cos = torch.from_numpy((np.cos(angles) * magnitude).astype(np.float32)).to(ctx.device)
+        self.sin = torch.from_numpy((np.sin(angles) * magnitude).astype(np.float32)).to(ctx.device)
 
     def tables(self):
         return self.cos, self.sin

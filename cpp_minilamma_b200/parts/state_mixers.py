@@ -12,6 +12,9 @@ write, and both normalise every head's o by its root mean square before a gate a
                      the last taps - 1 convolution inputs of a sequence are state too;
                      out = W_o (o / rms(o) * w * sigmoid(W_g2 W_g1 h))
 
+`gated_linear_attention`  a decay per head and key channel, g = sigmoid(W_a2 W_a1 h + b)^(1 / tau), u = v, q / sqrt(d);
+                     out = W_o (o / rms(o) * w * silu(W_g h))
+
 What enters the recurrence is float32 (decays, step sizes, gates, unit vectors, the state); the projections are
 products in the run's dtype.  Sizes, decays, tap counts and eps are parameters.
 """
@@ -197,5 +200,81 @@ class GatedDeltaRule(Mixer):
         return self.o.forward(step, gated, "o")
 
 
+class GatedLinearAttention(Mixer):
+    """params: n_heads, head_dim, v_head_dim, tau (the decay is sigmoid(z)^(1 / tau)), eps (of the head norm),
+    decay_rank (inner size of the low-rank pair, -1: as stored), out_name (workspace name of the result, default "o"),
+    names: tensor names for "q", "k", "v", "g", "a1", "a2", "a2_bias", "norm", "o"."""
+
+    capturable = True
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.n_heads = int(params["n_heads"])
+        self.d = int(params["head_dim"])
+        self.dv = int(params["v_head_dim"])
+        self.tau = float(params["tau"])
+        self.eps = float(params["eps"])
+        self.decay_rank = int(params.get("decay_rank") or -1)
+        self.names = dict(params["names"])
+        self.out_name = params.get("out_name") or "o"
+        if self.tau <= 0:
+            raise ValueError(f"gated linear attention: tau {self.tau} must be positive")
+        self.proj: Optional[Linear] = None   # q, k, v, g
+        self.low: Optional[Linear] = None    # a1
+        self.high: Optional[Linear] = None   # a2 over the columns of a1
+        self.o: Optional[Linear] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D, H, d, dv, n = self.ctx.hidden_size, self.n_heads, self.d, self.dv, self.names
+        return [WeightSpec(n["q"], (H * d, D)), WeightSpec(n["k"], (H * d, D)), WeightSpec(n["v"], (H * dv, D)),
+                WeightSpec(n["g"], (H * dv, D)), WeightSpec(n["a1"], (self.decay_rank, D)),
+                WeightSpec(n["a2"], (H * d, self.decay_rank)), WeightSpec(n["a2_bias"], (H * d,), kind="vector"),
+                WeightSpec(n["norm"], (dv,), kind="vector", init="norm"), WeightSpec(n["o"], (D, H * dv))]
+
+    def bind(self, store) -> None:
+        n = self.names
+        a1 = store.take(n["a1"])
+        a2 = store.take(n["a2"])
+        if a2.shape[1] != a1.shape[0]:
+            raise ValueError(f"gated linear attention: {n['a2']} reads {a2.shape[1]} inputs, {n['a1']} gives {a1.shape[0]}")
+        mats = _same_dtype([store.take(n[p]) for p in ("q", "k", "v", "g")])
+        self.proj = Linear(_pad_rows(torch.cat(mats, dim=0)), n["q"] + "+k+v+g")
+        a1, a2 = _same_dtype([a1, a2])
+        self.low = Linear(_pad_rows(a1), n["a1"])
+        # the second level over the first level's columns (and its padding)
+        high = torch.zeros((a2.shape[0], self.low.out_features), dtype=a2.dtype, device=a2.device)
+        high[:, :a2.shape[1]] = a2
+        self.high = Linear(_pad_rows(high), n["a2"])
+        del mats, a1, a2, high
+        self.bias = store.take(n["a2_bias"])
+        self.norm_w = store.take(n["norm"])
+        self.o = Linear(store.take(n["o"]), n["o"])
+
+    def parameter_bytes(self) -> int:
+        return sum(l.parameter_bytes() for l in (self.proj, self.low, self.high, self.o))
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(state=StateNeed((("S", (self.n_heads, self.d, self.dv)),)))
+
+    def forward(self, step, h, cache):
+        T, H, d, dv = h.shape[0], self.n_heads, self.d, self.dv
+        ws = step.ws
+        proj = self.proj.forward(step, h, "gla.proj")
+        low = self.low.forward(step, h, "gla.low")
+        rate = self.high.forward(step, low, "gla.rate", out_dtype=torch.float32)  # [T, H d (+ padding)]
+        q = ws.buffer("gla.q", (T, H * d), torch.float32)
+        k = ws.buffer("gla.k", (T, H * d), torch.float32)
+        v = ws.buffer("gla.v", (T, H * dv), torch.float32)
+        g = ws.buffer("gla.g", (T, H * d), torch.float32)
+        K.channel_decay_prepare(proj, rate, self.bias, q, k, v, g, H, d, dv, 1.0 / math.sqrt(d), self.tau)
+        o = ws.buffer("gla.o", (T, H * dv), torch.float32)
+        K.state_scan(q, k, v, g, None, None, cache.state["S"], o, step.seq_slot, step.seq_qstart, step.seq_qlen,
+                     step.n_seqs, H, H, d, dv)
+        gated = ws.buffer("gla.gated", (T, H * dv), self.ctx.act_dtype)
+        K.head_norm_gate(o, self.norm_w, proj, gated, H, dv, self.eps, K.GATE_SILU, gate_col=H * (2 * d + dv))
+        return self.o.forward(step, gated, self.out_name)
+
+
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "retention", Retention)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

@@ -487,6 +487,58 @@ def malulorn_rooflines(size, tokens, batch, context, peaks):
     return out
 
 
+def sopanex_config(size):
+    """Six layers, each with attention (learned sink, values that are the keys, 64 of 128 dimensions rotated under a
+    ramp) beside gated linear attention of half as many heads of 128, and 16 gelu experts of ff / 4 plus 2 pass-through
+    experts, 3 per token, beside a gated shared expert of ff / 2: the Malulorn decoder's sizes (same width, heads,
+    layer runs, expert count and widths), with the recurrent mixer on top."""
+    import cpp_minilamma_b200 as ml
+    s = DESIGN_SIZES[size]
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 3, "identity": 2, "scale": 2.0}, "expert": {"ff": s["ff"] // 4},
+           "shared": {"ff": s["ff"] // 2}}
+    layer = {"type": "parallel", "mlp": mlp,
+             "mixer": {"left_scale": 1.0, "right_scale": 1.0,
+                       "left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                "rot": {"base": 500000.0, "dims": 64,
+                                        "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 1.0}}},
+                       "right": {"heads": s["heads"] // 2, "dim": 128, "vdim": 128, "tau": 8.0, "decay_rank": 64}}}
+    return ml.config_from_dict({"architecture": "Sopanex", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+                                "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 33, "mul_cur": 5}},
+                                "layers": [layer] * (3 * s["groups"]), "torch_dtype": "bfloat16"})
+
+
+def sopanex_rooflines(size, tokens, batch, context, peaks):
+    """As `design_rooflines`, for the kernels of the Sopanex decoder and their like in the Malulorn decoder (and, for
+    the recurrent mixer, in the Kupirax decoder: `--design kupirax` measures those)."""
+    s = DESIGN_SIZES[size]
+    H, G, d, D, ff = s["heads"], s["kv_heads"], 128, s["width"], s["ff"]
+    Hr, dr, dvr = s["heads"] // 2, 128, 128
+    E, R, top, eff = 16, 18, 3, ff // 4
+    causal = tokens * (tokens + 1) // 2
+    out = {k: v for k, v in malulorn_rooflines(size, tokens, batch, context, peaks).items() if k[0] == "malulorn"}
+    out["sopanex", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * causal * 2 * d)
+    qk = (H * d + G * d) * 2
+    out["sopanex", "prefill", "local_attention_prepare"] = ("hbm", tokens * (qk + qk + G * d * 2))  # q, k rotated and v written
+    out["sopanex", "decode", "local_attention_prepare"] = ("hbm", batch * (qk + qk + G * d * 2))
+    out["sopanex", "decode", "attention_decode"] = ("hbm", batch * context * G * 2 * d * 2)
+    out["sopanex", "prefill", "moe_gate_up_mma"] = ("tensor", 2.0 * tokens * top * (E / R) * eff * D)  # a share of the choices passes through
+    out["sopanex", "prefill", "moe_down_mma"] = ("tensor", 2.0 * tokens * top * (E / R) * eff * D)
+    touched = min(E, batch * top)
+    out["sopanex", "decode", "moe_gate_up_mma"] = ("hbm", touched * eff * D * 2)
+    out["sopanex", "decode", "moe_down_mma"] = ("hbm", touched * eff * D * 2)
+    for kind, n, seqs in (("prefill", tokens, 1), ("decode", batch, batch)):
+        out["sopanex", kind, "moe_route"] = ("hbm", n * D * 2 + (R + 1) * D * 4)
+        out["sopanex", kind, "moe_combine"] = ("hbm", n * D * (top * 4 + 2 + 2 + 2))
+        out["sopanex", kind, "rmsnorm"] = ("hbm", n * D * (4 + 4 + 2 + 2 + 1))       # half of them add two deltas
+        out["sopanex", kind, "heads_gate"] = ("hbm", n * H * d * 4)
+        out["sopanex", kind, "embedding_pair"] = ("hbm", n * D * (2 + 2 + 4))
+        out["sopanex", kind, "activation"] = ("hbm", n * (ff // 2) * 4)
+        out["sopanex", kind, "state_scan (channel decay)"] = ("hbm", n * Hr * (3 * dr + 2 * dvr) * 4 + seqs * Hr * dr * dvr * 8)
+        out["sopanex", kind, "channel_decay_prepare"] = ("hbm", n * Hr * ((2 * dr + dvr) * 2 + dr * 4 + (3 * dr + dvr) * 4))
+        out["sopanex", kind, "head_norm_gate"] = ("hbm", n * Hr * dvr * (4 + 2 + 2))
+    return out
+
+
 def llama_like_config(size):
     import cpp_minilamma_b200 as ml
     s = DESIGN_SIZES[size]
@@ -553,7 +605,8 @@ def design_rooflines(size, tokens, batch, context, peaks):
 
 
 def bench_design(args):
-    """Prompt and decode throughput of the Kupirax or Malulorn decoder and of the Llama decoder at equal width,
+    """Prompt and decode throughput of the Kupirax or Malulorn decoder and of the Llama decoder (of the Sopanex decoder
+    and of the Malulorn decoder, the closest to it) at equal width,
     feed-forward, heads and layer count (random bfloat16 weights), and the device time of each of this library's kernels in one
     prompt step and one decode step of either, with the fraction of the measured peak it reaches."""
     import numpy as np
@@ -564,16 +617,17 @@ def bench_design(args):
     warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 8)
     tokens, batch, context = PREFILL_TOKENS, 64, 1024
     design = args.design
-    make_config = {"kupirax": kupirax_config, "malulorn": malulorn_config}[design]
-    rooflines = {"kupirax": design_rooflines, "malulorn": malulorn_rooflines}[design]
-    result = {"design": design, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+    make_config = {"kupirax": kupirax_config, "malulorn": malulorn_config, "sopanex": sopanex_config}[design]
+    rooflines = {"kupirax": design_rooflines, "malulorn": malulorn_rooflines, "sopanex": sopanex_rooflines}[design]
+    beside, beside_config = ("malulorn", malulorn_config) if design == "sopanex" else ("llama", llama_like_config)
+    result = {"design": design, "beside": beside, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
               "prefill_tokens": tokens, "decode_prompts": "uniform[128,1024)", "steps": steps, "warmup": warmup,
               "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": peaks["source"]},
               "sizes": {}}
     for size in ([args.size] if args.size else list(DESIGN_SIZES)):
         entry = {}
         expected = rooflines(size, tokens, batch, context, peaks)
-        for model, cfg in ((design, make_config(size)), ("llama", llama_like_config(size))):
+        for model, cfg in ((design, make_config(size)), (beside, beside_config(size))):
             llm = ml.random_model(cfg, seed=0, dtype="bfloat16", max_tokens=batch * 1536 + 8192, max_positions=4096,
                                   max_seqs=batch, max_step_tokens=8192)
             numbers = {"layers": len(llm.model.spec.schedule), "parameters": llm.model.parameter_count()}
@@ -634,9 +688,9 @@ def main():
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31_8b", help="model shape of the --profile step")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode step")
     parser.add_argument("--context", type=int, default=1024, help="prompt length of the --profile decode step")
-    parser.add_argument("--design", choices=["kupirax", "malulorn"], default=None,
+    parser.add_argument("--design", choices=["kupirax", "malulorn", "sopanex"], default=None,
                         help="instead of the default workload: prompt and decode throughput and kernel times of that "
-                             "decoder beside the Llama decoder at equal sizes")
+                             "decoder beside the Llama decoder (sopanex: beside the Malulorn decoder) at equal sizes")
     parser.add_argument("--size", choices=sorted(DESIGN_SIZES), default=None, help="one size of --design (default: all)")
     args = parser.parse_args()
 

@@ -40,6 +40,8 @@ struct DecodeMmaArgs {
   // 1: the softmax's denominator has one more term exp(0) that carries no value (a sink); it is counted once, by the
   // block that holds a sequence's first keys
   int sink;
+  // optional [Hq]: the sink's score per query head (natural units, not scaled) in place of 0
+  const float* sink_values;
 };
 
 __device__ __forceinline__ float2 unpack_bf162(unsigned r) {

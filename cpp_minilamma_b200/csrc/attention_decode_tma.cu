@@ -385,9 +385,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 
     float o[NT][4];
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8, this warp's keys only
-    if (a.sink && warp == 0 && split == 0) {  // the sink: as if one key that scores 0 and has no value had been seen
-      m_run[0] = m_run[1] = 0.f;
-      l_run[0] = l_run[1] = 1.f;
+    if (a.sink && warp == 0 && split == 0) {  // the sink: as if one key with a score of its own (0 unless given) and no
+      // value had been seen.  The sums are per lane and added over a row's four lanes after the loop: one lane counts it.
+      m_run[0] = a.sink_values ? a.sink_values[h0 + min(g, ng - 1)] : 0.f;
+      m_run[1] = a.sink_values ? a.sink_values[h0 + min(g + 8, ng - 1)] : 0.f;
+      l_run[0] = l_run[1] = t == 0 ? 1.f : 0.f;
     }
 
     if (warp == 4) {
@@ -647,7 +649,7 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                                 float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
                                 int max_blocks, int n_splits, int window, float scale, int* counters,
                                 int cluster_merge, const int* seq_order, const int* work, int work_pairs, int sink,
-                                cudaStream_t stream) {
+                                const float* sink_values, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
@@ -674,7 +676,8 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                        (const __nv_bfloat16*)qkv, fused ? cos_table : nullptr, fused ? sin_table : nullptr,
                        fused && write_kv ? (__nv_bfloat16*)k_cache : nullptr,
                        fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved, seq_order, work};
-  a.sink = sink ? 1 : 0;
+  a.sink = (sink || sink_values) ? 1 : 0;
+  a.sink_values = sink_values;
   const int rows = work != nullptr ? work_pairs : n_seqs;  // the grid's second index
   if (head_dim == 64)
     return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, rows, cluster_merge, stream)

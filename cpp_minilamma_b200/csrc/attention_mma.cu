@@ -31,7 +31,7 @@ MLL_API int mll_attn_decode_mma_supported(int dtype, int head_dim) {
 MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* v_cache, const int* seq_slot,
                                 const int* seq_ctx, const int* block_table, float* scratch, void* out, int n_seqs,
                                 int n_heads, int n_kv_heads, int head_dim, int max_blocks, int n_splits, int window,
-                                float scale, int* counters, int sink,
+                                float scale, int* counters, int sink, const float* sink_values,
                                 cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_mma_supported(MLL_BF16, head_dim), "attention decode (mma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (mma): bad head counts");
@@ -44,7 +44,8 @@ MLL_API int mll_attn_decode_mma(const void* q, const void* k_cache, const void* 
                        (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, n_splits, window, scale,
                        counters,
                        nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
-  a.sink = sink ? 1 : 0;
+  a.sink = (sink || sink_values) ? 1 : 0;
+  a.sink_values = sink_values;
   return mll::launch_decode_mma_any(a, head_dim, n_seqs, false, stream);
 }
 

@@ -95,8 +95,9 @@ attn_decode_mma_kernel(DecodeMmaArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8
-  if (a.sink && split == 0) {  // the sink: as if one key that scores 0 and has no value had been seen
-    m_run[0] = m_run[1] = 0.f;
+  if (a.sink && split == 0) {  // the sink: as if one key with a score of its own (0 unless given) and no value had been seen
+    m_run[0] = a.sink_values ? a.sink_values[h0 + min(g, ng - 1)] : 0.f;
+    m_run[1] = a.sink_values ? a.sink_values[h0 + min(g + 8, ng - 1)] : 0.f;
     l_run[0] = l_run[1] = 1.f;
   }
 

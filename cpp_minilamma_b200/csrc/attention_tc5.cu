@@ -66,6 +66,7 @@ struct PrefillTc5Args {
   int chunk;  // > 0: key j is visible from query i only if j / chunk == i / chunk (chunks count from position 0)
   float scale_log2;
   int sink;   // 1: the softmax's denominator has one more term exp(0), which carries no value
+  const float* sink_values;  // optional [Hq]: the sink's score per query head (natural units, not scaled) in place of 0
 };
 
 __device__ __forceinline__ unsigned a_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -454,7 +455,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
     const int qpos = pos0 + r;
     // the maximum that P and O are scaled by; the sum.  With a sink a row starts as if it had seen one key that
     // scores 0 and has no value.
-    float m_used = a.sink ? 0.f : -INFINITY, l_run = a.sink ? 1.f : 0.f;
+    float m_used = a.sink ? (a.sink_values ? a.sink_values[h] * 1.4426950408889634f : 0.f) : -INFINITY;  // log2 units
+    float l_run = a.sink ? 1.f : 0.f;
     for (int i = 0; i < n_pages; ++i) {
       const int sb = i % SB, st = i % KS;
       wait(bar(L::AB_S_FULL, sb), (i / SB) & 1);
@@ -623,7 +625,8 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
                                  const int* seq_ctx, const int* seq_qstart, const int* seq_qlen, const int* tile_seq,
                                  const int* tile_row0, const int* block_table, void* out, int n_tokens,
                                  long long n_pages, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
-                                 int max_blocks, int window, int chunk, float scale, int sink, cudaStream_t stream) {
+                                 int max_blocks, int window, int chunk, float scale, int sink,
+                                 const float* sink_values, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_prefill_tc5_supported(MLL_BF16, head_dim), "attention prefill (tcgen05): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention prefill (tcgen05): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_tokens >= 0 && (long long)n_tiles * n_heads < (1ll << 31),
@@ -640,7 +643,7 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
   if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
   mll::PrefillTc5Args a{seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                         (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f,
-                        sink ? 1 : 0};
+                        (sink || sink_values) ? 1 : 0, sink_values};
   if (head_dim == 64) return mll::launch_prefill_tc5<64>(qmap, kmap, vmap, a, n_tiles, stream);
   return mll::launch_prefill_tc5<128>(qmap, kmap, vmap, a, n_tiles, stream);
 }

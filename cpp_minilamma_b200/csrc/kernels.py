@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 31
+ABI_VERSION = 32
 MAX_TOP_K = 1024
 
 
@@ -697,6 +697,13 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_
 
 
 USE_TENSOR_CORE_DECODE = True  # tests switch these off to reach the general kernels at every size
+def _check_sink_values(sink_values, n_heads: int) -> None:
+    if sink_values is not None:
+        _need(sink_values, "attention sink values", torch.float32, 1)
+        if sink_values.shape[0] != n_heads:
+            raise KernelError(f"attention: {sink_values.shape[0]} sink values for {n_heads} heads")
+
+
 USE_TENSOR_CORE_PREFILL = True
 USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core prefill
 
@@ -704,15 +711,19 @@ USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core
 def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out, n_seqs: int,
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None,
-                     work: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False) -> None:
+                     work: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False,
+                     sink_values: Optional[torch.Tensor] = None) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
-    `sink` (bfloat16 tensor-core kernels only): one more term exp(0) in the softmax's denominator.
+    `sink` (bfloat16 tensor-core kernels only): one more term exp(0) in the softmax's denominator, or
+    exp(sink_values[head]) with `sink_values` (float32 [Hq], not scaled).
     `chunk` > 0 (not together with a window): the query sees the keys of its own chunk of that many positions only,
     chunks counted from position 0; the kernels take it as a negative window.
     bfloat16 runs on tensor cores (head sizes 16 .. 256 in steps of 16), float32 on the general kernel.
     `order`: optional int32 permutation of the sequences, longest context first; the TMA-fed kernel starts its
     blocks in that order so that short sequences fill the end of the launch (the others ignore it)."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
+    _check_sink_values(sink_values, n_heads)
+    sink = bool(sink or sink_values is not None)
     if chunk:
         if chunk < 0 or window:
             raise KernelError("attention decode: a chunk must be positive and comes without a window")
@@ -735,7 +746,7 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
     if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
                                                 block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
                                                 n_splits, window, scale, counters, _order(order, n_seqs), work,
-                                                sink=sink):
+                                                sink=sink, sink_values=sink_values):
         return
     if work is not None:
         raise KernelError("attention decode: a work list was given, but the kernel that takes one does not run here")
@@ -745,7 +756,8 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                                          ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                          ctypes.c_int(block_table.shape[1]), ctypes.c_int(n_splits),
                                          ctypes.c_int(window), ctypes.c_float(scale),
-                                         _ptr(counters if n_splits > 1 else None), ctypes.c_int(int(sink)), _stream()),
+                                         _ptr(counters if n_splits > 1 else None), ctypes.c_int(int(sink)),
+                                         _ptr(sink_values), _stream()),
                "attention_decode (tensor cores)")
         if n_splits > 1 and counters is None:
             _check(lib().mll_attn_combine(_ptr(scratch), _ptr(out), code, ctypes.c_int(n_seqs), ctypes.c_int(n_heads),
@@ -795,7 +807,7 @@ def _work(work, n_seqs: int, n_splits: int):
 
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
                 n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None, work=None,
-                sink: bool = False) -> bool:
+                sink: bool = False, sink_values: Optional[torch.Tensor] = None) -> bool:
     """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
     counters whenever the context is split); returns whether it did."""
     if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
@@ -812,7 +824,7 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
                                      ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _ptr(work),
                                      ctypes.c_int(work.shape[0] if work is not None else 0), ctypes.c_int(int(sink)),
-                                     _stream()),
+                                     _ptr(sink_values), _stream()),
            "attention_decode (TMA, work list)" if work is not None
            else "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
@@ -908,13 +920,17 @@ def attention_prefill_takes_chunks(dtype: torch.dtype, head_dim: int) -> bool:
 
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                       block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                      window: int, scale: float, wide_tiles=None, chunk: int = 0, sink: bool = False) -> None:
+                      window: int, scale: float, wide_tiles=None, chunk: int = 0, sink: bool = False,
+                      sink_values: Optional[torch.Tensor] = None) -> None:
     """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache.
     `wide_tiles`: (sequence, first row) int32 lists of the same rows in tiles of 128, which the tcgen05 kernel
     works on; without them it walks the 64-row list and every other block finds nothing to do.
     `chunk` > 0 (the tcgen05 kernel only; ask `attention_prefill_takes_chunks` first): key j is visible from query i
-    only if j // chunk == i // chunk.  `sink` (the same kernel only): one more term exp(0) in the softmax's denominator."""
+    only if j // chunk == i // chunk.  `sink` (the same kernel only): one more term exp(0) in the softmax's denominator,
+    or exp(sink_values[head]) with `sink_values` (float32 [Hq], not scaled)."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
+    _check_sink_values(sink_values, n_heads)
+    sink = bool(sink or sink_values is not None)
     for name, t in (("seq_slot", seq_slot), ("seq_ctx", seq_ctx), ("seq_qstart", seq_qstart),
                     ("seq_qlen", seq_qlen), ("tile_seq", tile_seq), ("tile_row0", tile_row0)):
         _need(t, f"attention {name}", torch.int32, 1)
@@ -936,7 +952,7 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
                                           ctypes.c_longlong(k_cache.shape[0]), ctypes.c_int(n_tiles),
                                           ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                           ctypes.c_int(block_table.shape[1]), ctypes.c_int(window), ctypes.c_int(chunk),
-                                          ctypes.c_float(scale), ctypes.c_int(int(sink)), _stream()),
+                                          ctypes.c_float(scale), ctypes.c_int(int(sink)), _ptr(sink_values), _stream()),
                "attention_prefill (tcgen05)")
         return
     if chunk or sink:
@@ -1029,13 +1045,6 @@ def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq,
         ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), ctypes.c_float(coef), ctypes.c_int(every),
         ctypes.c_int(int(v_from_k)), _stream()),
         "local_attention_prepare")
-
-
-def _check_sink_values(sink_values, n_heads: int) -> None:
-    if sink_values is not None:
-        _need(sink_values, "local attention sink values", torch.float32, 1)
-        if sink_values.shape[0] != n_heads:
-            raise KernelError(f"local attention: {sink_values.shape[0]} sink values for {n_heads} heads")
 
 
 def _check_local_caches(k_cache, v_cache, n_kv_heads: int, d: int, dv: int, v_in_k: bool) -> None:

@@ -636,3 +636,61 @@ def test_activation_kernel(dtype):
         K.activation(z, out, kind)
         tol = 1e-6 if dtype == torch.float32 else 8e-3
         assert ((out.cpu().double() - want).abs() <= tol * (1 + want.abs())).all()
+
+
+@pytest.mark.parametrize("learned", [True, False])
+@pytest.mark.parametrize("d", [32, 48, 64, 128])
+def test_sinks_in_the_kernels_shared_with_the_other_decoders(d, learned):
+    """Keys and values of one head size in bfloat16: prompts on the tcgen05 kernel (64, 128) and single tokens on the
+    TMA-fed (64, 128) or mma.sync decode kernel, with a sink per head (or the sink that scores 0), against the general
+    kernel.  Scores are small and the decoded contexts run from one key to hundreds, so the sink is most of a short
+    row's denominator: counted twice, or in the wrong units, it shows.  Decode runs with one block a sequence and
+    with the context split in four (the sink must be counted once)."""
+    from cpp_minilamma_b200.csrc import kernels as K
+    from cpp_minilamma_b200.engine.step import make_step_state
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device="cpu").manual_seed(d)
+    H, G = 6, 2
+    starts, lens = [0, 70, 129, 0, 0, 0, 0], [300, 200, 1, 1, 2, 5, 65]
+    n = len(lens)
+    ctxs = [s + m for s, m in zip(starts, lens)]
+    k_cache, v_cache, table = _paged(gen, ctxs, G, d, torch.bfloat16)
+    k_cache, v_cache, table = k_cache.to(dev), v_cache.to(dev), table.to(dev)
+    scale = 0.5 / d ** 0.5
+    T = sum(lens)
+    q = torch.randn((T, H * d), generator=gen).to(torch.bfloat16).to(dev)
+    sinks = torch.linspace(-3.0, 4.0, H).to(dev) if learned else None
+    state = make_step_state(dev, list(range(n)), starts, lens)
+    plain = torch.zeros((T, H * d), dtype=torch.bfloat16, device=dev)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, plain, H, G, d, d, 0, 0, scale,
+                      sink=True, sink_values=sinks)
+    without = torch.zeros_like(plain)
+    K.local_attention(q, k_cache, v_cache, state.tok_pos, state.tok_seq, state.seq_slot, table, without, H, G, d, d, 0, 0, scale)
+    torch.cuda.synchronize()
+    size = plain.float().abs().max().item()
+    assert (plain.float() - without.float()).abs().max().item() > 0.2 * size  # the sink matters in this test
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=dev)
+    if K.attention_prefill_takes_chunks(torch.bfloat16, d):
+        narrow = [(s, r) for s, m in enumerate(lens) for r in range(0, m, K.PREFILL_TILE)]
+        wide = sorted((starts[s] + min(m, r + 128), s, r) for s, m in enumerate(lens) for r in range(0, m, 128))
+        fast = torch.zeros_like(plain)
+        K.attention_prefill(q, k_cache, v_cache, state.seq_slot, state.seq_ctx, state.seq_qstart, state.seq_qlen,
+                            ints([s for s, _ in narrow]), ints([r for _, r in narrow]), table, fast, len(narrow), H, G, d, 0,
+                            scale, wide_tiles=(ints([s for _, s, _ in wide]), ints([r for _, _, r in wide])), sink=True,
+                            sink_values=sinks)
+        torch.cuda.synchronize()
+        assert K.take_device_error() == 0
+        assert (fast.float() - plain.float()).abs().max().item() <= 0.03 * size
+    last = [sum(lens[:i + 1]) - 1 for i in range(n)]  # single tokens: the last token of every sequence
+    q1 = q[last].contiguous()
+    one = make_step_state(dev, list(range(n)), [c - 1 for c in ctxs], [1] * n)
+    for splits in (1, 4):
+        out = torch.zeros((n, H * d), dtype=torch.bfloat16, device=dev)
+        scratch = torch.zeros((K.attention_decode_scratch_floats(n, H, d, splits),), device=dev) if splits > 1 else None
+        counters = torch.zeros((n * G,), dtype=torch.int32, device=dev) if splits > 1 else None
+        K.attention_decode(q1, k_cache, v_cache, one.seq_slot, one.seq_ctx, table, scratch, out, n, H, G, d, splits, 0, scale,
+                           counters=counters, sink=True, sink_values=sinks)
+        torch.cuda.synchronize()
+        assert K.take_device_error() == 0
+        err = (out.float() - plain[last].float()).abs().max(dim=1).values
+        assert err.max().item() <= 0.03 * size, (splits, err.tolist())

@@ -1360,12 +1360,18 @@ class MoePlan(NamedTuple):
     mma: bool
 
 
+MOE_TILE_ROWS_OVERRIDE: Optional[int] = None  # measurements only: 0, 1 or 2 picks the tensor-core tile at every size
+
+
 def moe_tile_rows(mma: bool, n_pairs: int = 1 << 30, n_experts: int = 1) -> int:
-    """Rows of a tile of the routed products: the plain kernels' size, or one of the tensor-core kernels' two - the
-    small one while an expert gets 16 rows or fewer on average (single tokens)."""
+    """Rows of a tile of the routed products: the plain kernels' size, or one of the tensor-core kernels' three - 16
+    rows while an expert gets 8 rows or fewer on average (single tokens), 32 rows up to 32 on average, else 128."""
     if not mma:
         return int(lib().mll_moe_simt_rows())
-    return int(lib().mll_moe_mma_rows(ctypes.c_int(int(n_pairs <= 16 * n_experts))))
+    if MOE_TILE_ROWS_OVERRIDE is not None:
+        return int(lib().mll_moe_mma_rows(ctypes.c_int(MOE_TILE_ROWS_OVERRIDE)))
+    small = 1 if n_pairs <= 8 * n_experts else (2 if n_pairs <= 32 * n_experts else 0)
+    return int(lib().mll_moe_mma_rows(ctypes.c_int(small)))
 
 
 def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:

@@ -8,7 +8,9 @@
 // four warps side by side on 64 weight rows, four stages, four such blocks a multiprocessor (256 weight rows, one
 // block a multiprocessor: the same time; two warps on 128 weight rows: a quarter slower).  Such a step streams every touched expert's weights once
 // for a handful of rows, and on the wide tile it was bound by the MMAs spent on empty rows (128-row tiles at batch 64:
-// 2 TB/s from a cold cache).
+// 2 TB/s from a cold cache).  Between 8 and 32 rows per expert on average a third instance has tiles of 32 rows (two MMA
+// row tiles a warp, otherwise the small one): with 16-row tiles the experts that got 17 rows or more take a second
+// tile each, and a few of those push the grid past the blocks that are resident at once - a second, nearly empty wave.
 //   gate_up  the 128 weight rows are 64 gate rows and the 64 up rows of the same activation columns; a warp's
 //            eight 8-column tiles are four of gate and the same four of up, so silu(gate) * up happens in the
 //            accumulator registers; rows are gathered from the step's tokens by (token, choice) pair.
@@ -30,6 +32,7 @@ struct MoeMmaShape {
 };
 using MoeMmaWide = MoeMmaShape<2, 8, 4, 2, 64, 3>;   // 128 rows x 128 weight rows: prompts
 using MoeMmaSmall = MoeMmaShape<1, 2, 1, 4, 64, 4>;  // 16 rows x 64 weight rows: single tokens
+using MoeMmaMedium = MoeMmaShape<2, 2, 1, 4, 64, 4>;  // 32 rows x 64 weight rows: single tokens, 8 to 32 rows an expert
 
 // KIND 0: down; 1: gate_up (silu(gate) * up); 2: up alone with gelu (erf form) - the layout of `down`, rows gathered
 // by token, the activation in the accumulators, bfloat16 out by place.
@@ -187,14 +190,17 @@ template <int KIND>
 int launch_moe_mma_rows(const MoeProductArgs& a, int max_tiles, int tile_rows, cudaStream_t stream) {
   if (tile_rows == MoeMmaWide::BM) return launch_moe_mma<KIND, 2, 8, 4, 2, 64, 3>(a, max_tiles, stream);
   if (tile_rows == MoeMmaSmall::BM) return launch_moe_mma<KIND, 1, 2, 1, 4, 64, 4>(a, max_tiles, stream);
-  mll_set_error("moe (mma): tiles of %d rows (known: %d, %d)", tile_rows, MoeMmaSmall::BM, MoeMmaWide::BM);
+  if (tile_rows == MoeMmaMedium::BM) return launch_moe_mma<KIND, 2, 2, 1, 4, 64, 4>(a, max_tiles, stream);
+  mll_set_error("moe (mma): tiles of %d rows (known: %d, %d, %d)", tile_rows, MoeMmaSmall::BM, MoeMmaMedium::BM, MoeMmaWide::BM);
   return -1;
 }
 
 }  // namespace mll
 
-// Rows of a tile: the wide instance (small = 0) or the one for steps with few rows per expert.
-MLL_API int mll_moe_mma_rows(int small) { return small ? mll::MoeMmaSmall::BM : mll::MoeMmaWide::BM; }
+// Rows of a tile: the wide instance (small = 0) or one of the two for steps with few rows per expert (1: 16 rows, 2: 32).
+MLL_API int mll_moe_mma_rows(int small) {
+  return small == 1 ? mll::MoeMmaSmall::BM : (small == 2 ? mll::MoeMmaMedium::BM : mll::MoeMmaWide::BM);
+}
 
 // bfloat16 only; rows of 16-byte words on both sides of both products.
 MLL_API int mll_moe_mma_supported(int width, int inter) { return width > 0 && inter > 0 && width % 8 == 0 && inter % 8 == 0; }

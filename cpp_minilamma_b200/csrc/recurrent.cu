@@ -387,7 +387,7 @@ int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
 template <int MODE>
 int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
   const int d = a.d;
-  const bool many = (long long)n_seqs * a.n_heads * a.dv >= (long long)mll_sm_count() * 512;
+  const bool many = (long long)n_seqs * a.n_heads * a.dv >= (long long)mll_sm_count() * 256;
   if (many && d <= 32) return launch_scan<32, 1, MODE>(a, n_seqs, stream);
   if (many && d <= 64) return launch_scan<64, 1, MODE>(a, n_seqs, stream);
   if (many && d <= 128) return launch_scan<64, 2, MODE>(a, n_seqs, stream);

@@ -521,8 +521,8 @@ def test_routed_feed_forward_kernels(dtype, T, E, top, D, F):
     sure = torch.ones(T, dtype=torch.bool) if margin is None else margin > 1e-4
     assert torch.equal(chosen.cpu().long()[sure], chosen_ref[sure])
     assert (weight.cpu().double()[sure] - w_ref[sure]).abs().max().item() < 1e-5
-    for mma, small in ([(False, False), (True, False), (True, True)] if K.moe_mma_supported(dtype, D, F) else [(False, False)]):
-        rows = K.moe_tile_rows(mma, 1 if small else 1 << 30, 1)  # the tensor-core kernels' tiles of 128 and of 16 rows
+    for mma, small in ([(False, 0), (True, 0), (True, 1), (True, 2)] if K.moe_mma_supported(dtype, D, F) else [(False, 0)]):
+        rows = K.moe_tile_rows(mma, (1 << 30, 1, 20)[small], 1)  # the tensor-core kernels' tiles of 128, 16 and 32 rows
         n_pairs = T * top
         tiles = K.moe_max_tiles(n_pairs, E, rows)
         ints = lambda n: torch.full((n,), -7, dtype=torch.int32, device=dev)

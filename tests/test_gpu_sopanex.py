@@ -599,8 +599,8 @@ def test_routed_kernels_with_scores_over_all_experts(dtype, T, E, I, top, D, F):
     K.moe_route(hd, router.to(dev), corr.to(dev), chosen2, weight2, top, logits=logits, all_scores=True, scale=scale, gate_out=gate2)
     torch.cuda.synchronize()
     assert torch.equal(chosen2.cpu()[sure], chosen.cpu()[sure]) and (gate2 - gate).abs().max().item() < 1e-5
-    for mma, small in ([(False, False), (True, False), (True, True)] if K.moe_mma_supported(dtype, D, F) else [(False, False)]):
-        rows = K.moe_tile_rows(mma, 1 if small else 1 << 30, 1)
+    for mma, small in ([(False, 0), (True, 0), (True, 1), (True, 2)] if K.moe_mma_supported(dtype, D, F) else [(False, 0)]):
+        rows = K.moe_tile_rows(mma, (1 << 30, 1, 20)[small], 1)  # the tensor-core kernels' tiles of 128, 16 and 32 rows
         n_pairs = T * top
         tiles = K.moe_max_tiles(n_pairs, R, rows)
         ints = lambda n: torch.full((n,), -7, dtype=torch.int32, device=dev)

@@ -224,14 +224,14 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 // `tok_stage` tokens at a time through a two-stage ring of asynchronous copies, so that the next tokens load
 // while these are worked on and the chain from token to token is arithmetic only.
 // MODE 0: one decay per head; 1: the delta rule with a decay per key channel; 2: a decay per key channel, u = v.
-template <int ROWS, int R, int MODE>
-__global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
+template <int ROWS, int R, int MODE, int THREADS>
+__global__ void __launch_bounds__(THREADS) state_scan_kernel(ScanArgs a) {
   constexpr bool DELTA = MODE == 1;    // beta and the correction by S^T k
   constexpr bool CHANNEL = MODE != 0;  // g per key channel travels with q and k
   extern __shared__ __align__(16) float stage[];
   constexpr int DP = ROWS * R;          // padded number of rows
   constexpr int CPW = 32 / R;           // columns per warp
-  constexpr int CPB = CPW * (SCAN_THREADS / 32);
+  constexpr int CPB = CPW * (THREADS / 32);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = lane / CPW, cw = lane % CPW;
   const int col0 = blockIdx.x * CPB;
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
   const int per_stage = (TS * DP * (CHANNEL ? 3 : 2) + TS * CPB + TS + 3) & ~3;  // stages start on 16-byte boundaries
   // the padding rows of both stages, once: the copies below never touch them
   if (d < DP)
-  for (int i = tid; i < 2 * TS * DP; i += SCAN_THREADS) {
+  for (int i = tid; i < 2 * TS * DP; i += THREADS) {
     const int st = i / (TS * DP), rest = i % (TS * DP);
     if (rest % DP >= d) {
       float* base = stage + st * per_stage;
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     float* b_s = v_s + TS * CPB;
     if ((d & 3) == 0) {  // rows are whole 16-byte words
       const int words = d >> 2;
-      for (int i = tid; i < nt * words; i += SCAN_THREADS) {
+      for (int i = tid; i < nt * words; i += THREADS) {
         const int tt = i / words, e = (i % words) << 2;
         const size_t tok = (size_t)(row0 + t0 + tt);
         cp_async16(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
         if (CHANNEL) cp_async16(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
       }
     } else {
-      for (int i = tid; i < nt * d; i += SCAN_THREADS) {
+      for (int i = tid; i < nt * d; i += THREADS) {
         const int tt = i / d, e = i % d;
         const size_t tok = (size_t)(row0 + t0 + tt);
         cp_async4(q_s + tt * DP + e, a.q + (tok * G + kvh) * d + e);
@@ -286,12 +286,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
         if (CHANNEL) cp_async4(g_s + tt * DP + e, a.g + (tok * H + h) * d + e);
       }
     }
-    for (int i = tid; i < nt * CPB; i += SCAN_THREADS) {
+    for (int i = tid; i < nt * CPB; i += THREADS) {
       const int tt = i / CPB, c = i % CPB;
       if (col0 + c < dv) cp_async4(v_s + i, a.v + ((size_t)(row0 + t0 + tt) * H + h) * dv + col0 + c);
     }
     if (DELTA)
-      for (int i = tid; i < nt; i += SCAN_THREADS) cp_async4(b_s + i, a.beta + (size_t)(row0 + t0 + i) * H + h);
+      for (int i = tid; i < nt; i += THREADS) cp_async4(b_s + i, a.beta + (size_t)(row0 + t0 + i) * H + h);
   };
   const float decay = CHANNEL ? 1.f : a.head_decay[h];
   load(0, 0);
@@ -312,40 +312,55 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
     const float* g_s = k_s + TS * DP;
     const float* v_s = stage + st * per_stage + TS * DP * (CHANNEL ? 3 : 2);
     const float* b_s = v_s + TS * CPB;
-    for (int tt = 0; tt < nt; ++tt) {
-      // this lane's rows of q, k and g as 16-byte words (ROWS and DP are multiples of 4)
-      float qv[ROWS], kv[ROWS], gv[CHANNEL ? ROWS : 1];
+    // Without the delta rule a token's output is off the chain from token to token (only S is carried), so four or eight
+    // tokens go through the update one after another and their outputs' sums over the lanes of a column are then formed
+    // side by side: independent chains of shuffles instead of one a token.
+    constexpr int TU = (!DELTA && R >= 8) ? (ROWS <= 4 ? 8 : 4) : 1;
+    for (int tt = 0; tt < nt; tt += TU) {
+      float o_part[TU];
 #pragma unroll
-      for (int i = 0; i < ROWS; i += 4) {
-        *reinterpret_cast<float4*>(qv + i) = *reinterpret_cast<const float4*>(q_s + tt * DP + r * ROWS + i);
-        *reinterpret_cast<float4*>(kv + i) = *reinterpret_cast<const float4*>(k_s + tt * DP + r * ROWS + i);
-        if (CHANNEL) *reinterpret_cast<float4*>(gv + i) = *reinterpret_cast<const float4*>(g_s + tt * DP + r * ROWS + i);
-      }
-      float u = live ? v_s[tt * CPB + warp * CPW + cw] : 0.f;
-      if (DELTA) {
-        float p4[4] = {0.f, 0.f, 0.f, 0.f};  // four sums side by side: the chain of additions is a quarter as long
+      for (int j = 0; j < TU; ++j) {
+        o_part[j] = 0.f;
+        const int tj = tt + j;
+        if (TU > 1 && tj >= nt) continue;  // the same for every thread of the block
+        // this lane's rows of q, k and g as 16-byte words (ROWS and DP are multiples of 4)
+        float qv[ROWS], kv[ROWS], gv[CHANNEL ? ROWS : 1];
+#pragma unroll
+        for (int i = 0; i < ROWS; i += 4) {
+          *reinterpret_cast<float4*>(qv + i) = *reinterpret_cast<const float4*>(q_s + tj * DP + r * ROWS + i);
+          *reinterpret_cast<float4*>(kv + i) = *reinterpret_cast<const float4*>(k_s + tj * DP + r * ROWS + i);
+          if (CHANNEL) *reinterpret_cast<float4*>(gv + i) = *reinterpret_cast<const float4*>(g_s + tj * DP + r * ROWS + i);
+        }
+        float u = live ? v_s[tj * CPB + warp * CPW + cw] : 0.f;
+        if (DELTA) {
+          float p4[4] = {0.f, 0.f, 0.f, 0.f};  // four sums side by side: the chain of additions is a quarter as long
+#pragma unroll
+          for (int i = 0; i < ROWS; ++i) {
+            s[i] *= gv[i];
+            p4[i & 3] = fmaf(s[i], kv[i], p4[i & 3]);
+          }
+          float part = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+#pragma unroll
+          for (int o = CPW; o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+          u = b_s[tj] * (u - part);
+        }
+        float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-          s[i] *= gv[i];
-          p4[i & 3] = fmaf(s[i], kv[i], p4[i & 3]);
+          if (MODE == 1) s[i] = fmaf(kv[i], u, s[i]);
+          else if (MODE == 2) s[i] = fmaf(gv[i], s[i], kv[i] * u);
+          else s[i] = fmaf(decay, s[i], kv[i] * u);
+          o4[i & 3] = fmaf(s[i], qv[i], o4[i & 3]);
         }
-        float part = (p4[0] + p4[1]) + (p4[2] + p4[3]);
-#pragma unroll
-        for (int o = CPW; o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-        u = b_s[tt] * (u - part);
+        o_part[j] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
       }
-      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < ROWS; ++i) {
-        if (MODE == 1) s[i] = fmaf(kv[i], u, s[i]);
-        else if (MODE == 2) s[i] = fmaf(gv[i], s[i], kv[i] * u);
-        else s[i] = fmaf(decay, s[i], kv[i] * u);
-        o4[i & 3] = fmaf(s[i], qv[i], o4[i & 3]);
-      }
-      float o_part = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+      for (int o = CPW; o < 32; o <<= 1)
 #pragma unroll
-      for (int o = CPW; o < 32; o <<= 1) o_part += __shfl_xor_sync(0xffffffffu, o_part, o);
-      if (live && r == 0) a.out[((size_t)(row0 + t0 + tt) * H + h) * dv + col] = o_part;
+        for (int j = 0; j < TU; ++j) o_part[j] += __shfl_xor_sync(0xffffffffu, o_part[j], o);
+#pragma unroll
+      for (int j = 0; j < TU; ++j)
+        if (live && r == 0 && tt + j < nt) a.out[((size_t)(row0 + t0 + tt + j) * H + h) * dv + col] = o_part[j];
     }
     __syncthreads();  // this stage is loaded again two rounds on
   }
@@ -358,21 +373,21 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(ScanArgs a) {
   }
 }
 
-template <int ROWS, int R, int MODE>
+template <int ROWS, int R, int MODE, int THREADS = SCAN_THREADS>
 int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
   ScanArgs a = args;
-  constexpr int DP = ROWS * R, CPB = (32 / R) * (SCAN_THREADS / 32);
+  constexpr int DP = ROWS * R, CPB = (32 / R) * (THREADS / 32);
   a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : (DP <= 512 ? 4 : 2));
   const size_t smem = (size_t)2 * ((a.tok_stage * DP * (MODE ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
   const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
   if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, MODE, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) {
       mll_set_error("state scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
       return (int)err;
     }
   }
-  MLL_LAUNCH((state_scan_kernel<ROWS, R, MODE>), grid, SCAN_THREADS, smem, stream, a);
+  MLL_LAUNCH((state_scan_kernel<ROWS, R, MODE, THREADS>), grid, THREADS, smem, stream, a);
   MLL_LAUNCH_CHECK();
   return 0;
 }
@@ -392,6 +407,15 @@ int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
   if (many && d <= 64) return launch_scan<64, 1, MODE>(a, n_seqs, stream);
   if (many && d <= 128) return launch_scan<64, 2, MODE>(a, n_seqs, stream);
   if (many && d <= 256) return launch_scan<64, 4, MODE>(a, n_seqs, stream);
+  // So few columns that eight lanes a column leave a multiprocessor with two or three warps (one prompt of a model a
+  // few thousand wide), each of which waits out the latency of its own instructions: a whole warp a column (half a
+  // warp for keys up to 64) - four rows a lane, a quarter of the arithmetic in every step of the chain from token to
+  // token - and eight warps a block, so that a block still stages a token's q, k and g once for eight columns.
+  // Not for the delta rule, whose sum over a column's lanes lies on the chain.
+  const bool few = MODE != 1 && (long long)n_seqs * a.n_heads * a.dv < (long long)mll_sm_count() * 16;
+  if (few && d > 32 && d <= 64) return launch_scan<4, 16, MODE, 256>(a, n_seqs, stream);
+  if (few && d > 64 && d <= 128) return launch_scan<4, 32, MODE, 256>(a, n_seqs, stream);
+  if (few && d > 128 && d <= 256) return launch_scan<8, 32, MODE, 256>(a, n_seqs, stream);
   if (d <= 32) return launch_scan<4, 8, MODE>(a, n_seqs, stream);
   if (d <= 64) return launch_scan<8, 8, MODE>(a, n_seqs, stream);
   if (d <= 128) return launch_scan<16, 8, MODE>(a, n_seqs, stream);

@@ -280,6 +280,8 @@ def test_tensor_core_prompt_kernel_against_the_general_one(d, dv, chunk, window)
                                              (96, 8, 4, 20, 100),      # a batch that fills the device: a thread a column
                                              (80, 8, 8, 72, 136),      # ... two lanes a column
                                              (40, 8, 2, 200, 256),     # ... four lanes a column
+                                             (3, 1, 1, 48, 40), (3, 2, 1, 72, 40), (3, 2, 2, 200, 24),  # very few (no delta rule): a warp or half a warp a column
+                                             (30, 8, 4, 72, 40), (20, 4, 2, 200, 40),  # in between: eight lanes, keys of 128 and 256
                                              (2, 1, 1, 300, 8)])       # keys beyond 256
 def test_state_scan_against_the_recurrence_written_out(delta, n_seqs, H, G, d, dv):
     """The scan kernel alone, both rules and every way it spreads a column over lanes: sequences of one to four

@@ -491,7 +491,8 @@ def test_norm_kernel_with_a_normed_delta(width):
         assert (out.cpu().double() - want).abs().max().item() < 3e-5
 
 
-@pytest.mark.parametrize("H,d,dv", [(2, 8, 12), (3, 6, 10), (1, 64, 64), (2, 128, 32), (4, 32, 128), (1, 40, 8)])
+@pytest.mark.parametrize("H,d,dv", [(2, 8, 12), (3, 6, 10), (1, 64, 64), (2, 128, 32), (4, 32, 128), (1, 40, 8), (1, 200, 24),
+                                    (8, 128, 128), (8, 64, 128), (4, 200, 256)])  # the last three: eight lanes a column; before them a warp or half a warp
 def test_channel_decay_recurrence(H, d, dv):
     """channel_decay_prepare + state_scan + head_norm_gate against the recurrence walked token by token in float64:
     three sequences of 150, 1 and 37 tokens, two of which go on from a state that is not zero; decays from quick

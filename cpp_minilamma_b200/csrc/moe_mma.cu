@@ -8,7 +8,7 @@
 // four warps side by side on 64 weight rows, four stages, four such blocks a multiprocessor (256 weight rows, one
 // block a multiprocessor: the same time; two warps on 128 weight rows: a quarter slower).  Such a step streams every touched expert's weights once
 // for a handful of rows, and on the wide tile it was bound by the MMAs spent on empty rows (128-row tiles at batch 64:
-// 2 TB/s from a cold cache).  Between 8 and 32 rows per expert on average a third instance has tiles of 32 rows (two MMA
+// 2 TB/s from a cold cache).  Between 12 and 32 rows per expert on average a third instance has tiles of 32 rows (two MMA
 // row tiles a warp, otherwise the small one): with 16-row tiles the experts that got 17 rows or more take a second
 // tile each, and a few of those push the grid past the blocks that are resident at once - a second, nearly empty wave.
 //   gate_up  the 128 weight rows are 64 gate rows and the 64 up rows of the same activation columns; a warp's
@@ -32,7 +32,7 @@ struct MoeMmaShape {
 };
 using MoeMmaWide = MoeMmaShape<2, 8, 4, 2, 64, 3>;   // 128 rows x 128 weight rows: prompts
 using MoeMmaSmall = MoeMmaShape<1, 2, 1, 4, 64, 4>;  // 16 rows x 64 weight rows: single tokens
-using MoeMmaMedium = MoeMmaShape<2, 2, 1, 4, 64, 4>;  // 32 rows x 64 weight rows: single tokens, 8 to 32 rows an expert
+using MoeMmaMedium = MoeMmaShape<2, 2, 1, 4, 64, 4>;  // 32 rows x 64 weight rows: single tokens, 12 to 32 rows an expert
 
 // KIND 0: down; 1: gate_up (silu(gate) * up); 2: up alone with gelu (erf form) - the layout of `down`, rows gathered
 // by token, the activation in the accumulators, bfloat16 out by place.

@@ -396,9 +396,11 @@ int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
 // thread holds a whole column (keys up to 64; two lanes up to 128, four up to 256: 64 rows are what a thread's
 // registers hold): a warp then reads and writes 128, 64 or 32 consecutive bytes of a row of the state.  Measured
 // on 128 sequences of 16 heads of 128 x 128 (134 MB of state in and out): 64 rows a lane 112 us (2.4 TB/s); 32
-// rows a lane and four lanes a column, with twice the resident blocks, 142 us.  Otherwise (a prompt of one or a few
-// sequences) eight lanes share a column, so that eight times as many threads work on the chain from token
-// to token.
+// rows a lane and four lanes a column, with twice the resident blocks, 142 us.  That layout starts at 256 columns a
+// multiprocessor (64 sequences of 8 heads of 128 value columns: 51 us with eight lanes a column, whose 16-byte pieces
+// of a row use half of every sector, 29 us with two).  Otherwise (a prompt of one or a few sequences) eight lanes
+// share a column, so that eight times as many threads work on the chain from token to token - or, with very few
+// columns, a whole warp (below).
 template <int MODE>
 int dispatch_scan(const ScanArgs& a, int n_seqs, cudaStream_t stream) {
   const int d = a.d;

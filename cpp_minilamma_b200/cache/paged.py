@@ -10,7 +10,8 @@
   is all the memory the cache ever needs, however the tokens are spread over sequences.
 * A **group** gathers the schedule entries whose mixers declare the same need
   (kv heads, head size, window).  Each group has storage and a block table of its own.
-  A group with a window w gives pages back as soon as no later query can read them.
+  A group with a window w gives pages back as soon as no later query can read them - except the pages of the
+  sequence's first `keep_first` positions, where the need says that those stay visible.
 * **State** is per-slot storage of fixed size for mixers that keep a running state
   instead of (or beside) keys and values: `state[name] [slots, *shape]`, float32 (or int32), zeroed
   when the slot is handed out.  An embedding that looks back one token keeps that token here too.
@@ -141,8 +142,9 @@ class CacheGroup:
         if self.need.window > 0:
             # the earliest query of this step sits at old_len and reads keys > old_len - window
             first_needed = max(0, old_len - self.need.window + 1) // PAGE
+            kept = (self.need.keep_first + PAGE - 1) // PAGE  # pages of the positions that stay visible
             gone = []
-            for b in range(min(first_needed, len(self.pages[slot]))):
+            for b in range(kept, min(first_needed, len(self.pages[slot]))):
                 if self.pages[slot][b] is not None:
                     gone.append(self.pages[slot][b])
                     self.pages[slot][b] = None

@@ -3,3 +3,4 @@ from .base import (ConfigError, ModelConfig, config_from_dict, known_architectur
 from .llama import LlamaConfig, RopeScaling
 from .kupirax import KupiraxConfig
 from .sopanex import SopanexConfig
+from .badolix import BadolixConfig

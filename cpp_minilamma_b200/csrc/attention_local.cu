@@ -8,6 +8,9 @@
 // exp(0) in the denominator that carries no value, so a row's weights may sum to less than one).  The values
 // may be the leading dv columns of the key rows (v_ld = d: a layer that caches one latent row per position and
 // reads it as key and as value); otherwise they have pages of their own (v_ld = dv).
+// A window may keep the sequence's first tokens (`keep_first`: key j < keep_first stays visible whatever its distance, at
+// its own position), and a score may be capped smoothly (s <- cap * tanh(s / cap) after the scale).  A layer that reads
+// another layer's keys and values prepares its queries only (`write_kv` 0).
 //
 // Two kernels, for prompts and single tokens alike:
 //   * prepare: one block per token.  q and k are each divided by the root mean square of their whole
@@ -40,13 +43,14 @@ struct LocalPrepArgs {
   int q_temp_every;
   int v_col;              // column of a row where the values begin: behind k, or k's own columns (values that are
                           // the keys as projected, before norm and rotation)
+  int write_kv;           // 0: the row holds queries only; nothing goes to the cache (another layer's is read)
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) local_prepare_kernel(LocalPrepArgs a) {
   __shared__ float scratch[32];
   const int t = blockIdx.x;
-  const int d = a.d, nq = a.n_heads * d, nk = a.n_kv_heads * d, nv = a.n_kv_heads * a.dv;
+  const int d = a.d, nq = a.n_heads * d, nk = a.write_kv ? a.n_kv_heads * d : 0, nv = a.write_kv ? a.n_kv_heads * a.dv : 0;
   const T* row = (const T*)a.qkv + (size_t)t * a.ld;
   float fq = 1.f, fk = 1.f;
   if (a.q_weight) {
@@ -67,7 +71,7 @@ __global__ void __launch_bounds__(256) local_prepare_kernel(LocalPrepArgs a) {
   const int pos = a.tok_pos[t];
   if (a.q_temp_every > 0) fq *= 1.f + a.q_temp_coef * logf((float)((pos + 1) / a.q_temp_every) + 1.f);
   const int slot = a.seq_slot[a.tok_seq[t]];
-  const int page = a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE];
+  const int page = a.write_kv ? a.block_table[(size_t)slot * a.max_blocks + pos / MLL_PAGE] : 0;
   const int in_page = pos % MLL_PAGE;
   const int half = a.rot >> 1;
   const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
@@ -142,6 +146,8 @@ struct LocalAttnArgs {
   int sink;              // 1: the softmax's denominator has one more term exp(sink value)
   const float* sink_values;  // [Hq] the sink's score per query head (unscaled), or null: 0
   int v_ld;              // elements between value rows: dv, or d when the values are the keys' leading columns
+  int keep_first;        // with a window: keys at positions below this stay visible
+  float softcap;         // > 0: score <- softcap * tanh(score / softcap)
 };
 
 // grid (tokens, Hk * head chunks), 128 threads.  A block owns one token, one kv head and up to `hpb` of the
@@ -194,13 +200,21 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
   for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
   const int p_begin = first / MLL_PAGE, p_end = pos / MLL_PAGE + 1;
+  // the kept first tokens that lie in front of the window: keys [0, kept), on the pages in front of p_begin and on
+  // p_begin itself (whose rows between `kept` and `first` are then skipped)
+  const int kept = (a.window > 0 && a.keep_first > 0) ? min(a.keep_first, first) : 0;
+  const int n_kept_pages = min((kept + MLL_PAGE - 1) / MLL_PAGE, p_begin);  // walked before p_begin
+  auto page_of = [&](int walk) { return walk < n_kept_pages ? walk : p_begin + (walk - n_kept_pages); };
+  const int n_walk = n_kept_pages + (p_end - p_begin);
   auto load_tiles = [&](int page_index, int stage) {
     const int page = table[page_index];
     const T* kg = (const T*)a.k_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * d;
     const T* vg = (const T*)a.v_cache + ((size_t)page * a.n_kv_heads + kvh) * MLL_PAGE * a.v_ld;
     T* kd = k_s + stage * k_tile;
     T* vd = v_s + stage * v_tile;
-    const int r_lo = max(0, first - page_index * MLL_PAGE), r_hi = min(MLL_PAGE, pos + 1 - page_index * MLL_PAGE);
+    // every row up to the last visible one is loaded when kept keys share the page; the scores mask the gap
+    const int r_lo = page_index * MLL_PAGE < kept ? 0 : max(0, first - page_index * MLL_PAGE);
+    const int r_hi = min(MLL_PAGE, pos + 1 - page_index * MLL_PAGE);
     if (vec) {
       const int kc = d / PAD, vc = dv / PAD;
       for (int c = tid; c < (r_hi - r_lo) * kc; c += 128) {
@@ -223,12 +237,13 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
     }
   };
 
-  load_tiles(p_begin, 0);
+  load_tiles(page_of(0), 0);
   cp_async_commit();
-  for (int p = p_begin, it = 0; p < p_end; ++p, ++it) {
+  for (int it = 0; it < n_walk; ++it) {
+    const int p = page_of(it);
     const int cur = stages == 2 ? (it & 1) : 0;
-    if (stages == 2 && p + 1 < p_end) {
-      load_tiles(p + 1, cur ^ 1);
+    if (stages == 2 && it + 1 < n_walk) {
+      load_tiles(page_of(it + 1), cur ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -237,12 +252,13 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
     __syncthreads();
     const T* kt = k_s + cur * k_tile;
     const T* vt = v_s + cur * v_tile;
-    const int jlo = max(0, first - p * MLL_PAGE), jhi = min(MLL_PAGE, pos + 1 - p * MLL_PAGE);
+    const int jlo = p * MLL_PAGE < kept ? 0 : max(0, first - p * MLL_PAGE), jhi = min(MLL_PAGE, pos + 1 - p * MLL_PAGE);
 
     for (int idx = tid; idx < ng * MLL_PAGE; idx += 128) {
       const int g = idx / MLL_PAGE, j = idx % MLL_PAGE;
       float sc = -INFINITY;
-      if (j >= jlo && j < jhi) {
+      const int kpos = p * MLL_PAGE + j;
+      if (j >= jlo && j < jhi && (kpos >= first || kpos < kept)) {
         const T* kr = kt + (size_t)j * k_stride;
         const float* qg = q_s + g * d_pad;
         float dot = 0.f;
@@ -256,7 +272,7 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
         } else {
           for (int e = 0; e < d; ++e) dot = fmaf(qg[e], to_float(kr[e]), dot);
         }
-        sc = dot;
+        sc = a.softcap > 0.f ? a.softcap * tanhf(dot / a.softcap) : dot;
       }
       s_s[idx] = sc;
     }
@@ -289,8 +305,8 @@ __global__ void __launch_bounds__(128) local_attention_kernel(LocalAttnArgs a, i
       }
     }
     __syncthreads();
-    if (stages == 1 && p + 1 < p_end) {
-      load_tiles(p + 1, 0);
+    if (stages == 1 && it + 1 < n_walk) {
+      load_tiles(page_of(it + 1), 0);
       cp_async_commit();
     }
   }
@@ -350,19 +366,19 @@ MLL_API int mll_local_attention_prepare(const void* qkv, const float* q_weight, 
                                         const int* tok_seq, const int* seq_slot, const int* block_table, void* q_out,
                                         void* k_cache, void* v_cache, int dtype, int n_tokens, int ld, int n_heads,
                                         int n_kv_heads, int d, int dv, int rot, int interleaved, int max_blocks,
-                                        float eps, float q_temp_coef, int q_temp_every, int v_from_k,
+                                        float eps, float q_temp_coef, int q_temp_every, int v_from_k, int write_kv,
                                         cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && d > 0 && dv > 0, "local attention prepare: bad sizes");
   MLL_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "local attention prepare: %d rotated dimensions of %d", rot, d);
   MLL_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "local attention prepare: one norm weight without the other");
-  MLL_REQUIRE(ld >= n_heads * d + n_kv_heads * (v_from_k ? d : d + dv), "local attention prepare: row stride %d too short", ld);
+  MLL_REQUIRE(ld >= n_heads * d + (write_kv ? n_kv_heads * (v_from_k ? d : d + dv) : 0), "local attention prepare: row stride %d too short", ld);
   MLL_REQUIRE(!v_from_k || dv == d, "local attention prepare: values that are the keys need dv == d, got %d / %d", dv, d);
   MLL_REQUIRE(q_temp_every >= 0, "local attention prepare: negative temperature period");
   if (n_tokens == 0) return 0;
   mll::LocalPrepArgs a{qkv, q_weight, k_weight, rot > 0 ? cos_table : nullptr, sin_table, tok_pos, tok_seq, seq_slot,
                        block_table, q_out, k_cache, v_cache, ld, n_heads, n_kv_heads, d, dv, rot, interleaved,
                        max_blocks, eps, q_temp_coef, q_temp_every,
-                       v_from_k ? n_heads * d : n_heads * d + n_kv_heads * d};
+                       v_from_k ? n_heads * d : n_heads * d + n_kv_heads * d, write_kv ? 1 : 0};
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::local_prepare_kernel<float>), n_tokens, 256, 0, stream, a);
   else if (dtype == MLL_BF16)
@@ -377,15 +393,16 @@ MLL_API int mll_local_attention(const void* q, const void* k_cache, const void* 
                                 const int* tok_seq, const int* seq_slot, const int* block_table, void* out, int dtype,
                                 int n_tokens, int n_heads, int n_kv_heads, int d, int dv, int chunk, int window,
                                 int max_blocks, float scale, int sink, const float* sink_values, int v_in_k,
-                                cudaStream_t stream) {
+                                int keep_first, float softcap, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention: bad head counts");
   MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0 && dv <= 1024, "local attention: head sizes %d / %d (at most 1024)", d, dv);
-  MLL_REQUIRE(chunk >= 0 && window >= 0, "local attention: negative chunk or window");
+  MLL_REQUIRE(chunk >= 0 && window >= 0 && keep_first >= 0 && softcap >= 0.f, "local attention: negative chunk, window, kept tokens or cap");
+  MLL_REQUIRE(keep_first == 0 || chunk == 0, "local attention: kept first tokens go with a window, not with chunks");
   MLL_REQUIRE(!v_in_k || dv <= d, "local attention: values of %d cannot be the leading columns of keys of %d", dv, d);
   if (n_tokens == 0) return 0;
   mll::LocalAttnArgs a{q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_tokens, n_heads,
                        n_kv_heads, d, dv, chunk, window, max_blocks, scale, (sink || sink_values) ? 1 : 0, sink_values,
-                       v_in_k ? d : dv};
+                       v_in_k ? d : dv, keep_first, softcap};
   if (dtype == MLL_F32) return mll::launch_local_attention<float>(a, stream);
   if (dtype == MLL_BF16) return mll::launch_local_attention<__nv_bfloat16>(a, stream);
   MLL_REQUIRE(false, "local attention: unknown dtype %d", dtype);

@@ -3,7 +3,9 @@
 // an explicit scale, and the chunk mask (key j visible from query i iff j <= i and j / chunk == i / chunk).
 // The kernel is instantiated for padded sizes DK, DV in {32, 64, 128, 256}; the real d and dv (multiples of
 // 8, so that rows are whole 16-byte words) are runtime values and the padding columns are zero-filled in
-// shared memory.  A tile starts at the first page that its first row's chunk (or window) reaches.
+// shared memory.  A tile starts at the first page that its first row's chunk (or window) reaches.  With a window that
+// keeps the sequence's first tokens (`keep_first`) the pages of those tokens are walked first, then the window's; a
+// capped score is cap * tanh(scale * s / cap).
 //
 // The same kernel serves steps of single tokens (`heads_as_rows`): a block then takes one sequence and one kv head,
 // and its rows are the query heads of that kv head's group (up to 64 a block), all at the sequence's last
@@ -37,6 +39,9 @@ struct LocalMmaArgs {
   int n_splits;                  // heads_as_rows only: blocks per (sequence, kv head, head chunk) along the context
   float* part_o;                 // [sequences, heads, n_splits, dv] unnormalised results (n_splits > 1)
   float* part_ml;                // [sequences, heads, n_splits, 2] maximum (log2 units) and sum
+  int keep_first;                // with a window: keys at positions below this stay visible
+  float softcap;                 // > 0: score <- softcap * tanh(score / softcap), in natural units
+  float scale;                   // the scale in natural units (scale_log2 = scale * log2 e)
 };
 
 template <int DK, int DV>
@@ -109,13 +114,19 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
   const int last_pos = pos0 + (rows - 1) * pos_step;
   const int last_chunk_start = a.chunk > 0 ? (last_pos / a.chunk) * a.chunk : 0;
   const int p_first = first_key / MLL_PAGE, p_last = last_pos / MLL_PAGE;
-  int pb = p_first, pe = p_last;  // this block's run of pages
+  // kept first tokens in front of the window: their pages are walked before the window's.  The walk's index w stands
+  // for page w below n_kept and for page p_first + (w - n_kept) from there on.
+  const int kept = (a.window > 0 && a.keep_first > 0) ? min(a.keep_first, first_key) : 0;
+  const int n_kept = min((kept + MLL_PAGE - 1) / MLL_PAGE, p_first);
+  auto page_at = [&](int w) { return w < n_kept ? w : p_first + (w - n_kept); };
+  const int w_last = n_kept + (p_last - p_first);
+  int pb = 0, pe = w_last;  // this block's run of the walk
   if (a.n_splits > 1) {
-    const int per = (p_last - p_first + a.n_splits) / a.n_splits;
-    pb = p_first + (int)blockIdx.z * per;
-    pe = min(p_last, pb + per - 1);
+    const int per = (w_last + a.n_splits) / a.n_splits;
+    pb = (int)blockIdx.z * per;
+    pe = min(w_last, pb + per - 1);
   }
-  if (pb <= pe) load_page(pb, 0);
+  if (pb <= pe) load_page(page_at(pb), 0);
   cp_async_commit();
 
   unsigned qf[KSTEPS][4];
@@ -135,18 +146,19 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     }
   }
 
-  for (int p = pb; p <= pe; ++p) {
-    const int stage = (p - pb) & 1;
+  for (int w = pb; w <= pe; ++w) {
+    const int p = page_at(w);
+    const int stage = (w - pb) & 1;
     cp_async_wait<0>();
     __syncthreads();
-    if (p == pb) {
+    if (w == pb) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks)
         ldmatrix_x4(qf[ks], q_s + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * L::KS + ks * 16 +
                                 ((lane >> 4) << 3));
       __syncthreads();
     }
-    if (p < pe) load_page(p + 1, stage ^ 1);
+    if (w < pe) load_page(page_at(w + 1), stage ^ 1);
     cp_async_commit();
     const __nv_bfloat16* kt = kv_s + (size_t)stage * stage_elems;
     const __nv_bfloat16* vt = v_in_k ? kt : kt + L::KTILE;
@@ -175,12 +187,13 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float v = s_acc[n][i] * a.scale_log2;
+        float v = a.softcap > 0.f ? a.softcap * 1.4426950408889634f * tanhf(s_acc[n][i] * a.scale / a.softcap)
+                                  : s_acc[n][i] * a.scale_log2;
         if (needs_mask) {
           const int row = warp * 16 + g + ((i >> 1) << 3);
           const int qpos = pos0 + row * pos_step;
           const int kpos = p * MLL_PAGE + n * 8 + 2 * t + (i & 1);
-          const bool ok = row < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window) &&
+          const bool ok = row < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window || kpos < a.keep_first) &&
                           (a.chunk <= 0 || kpos >= (qpos / a.chunk) * a.chunk);
           v = ok ? v : -INFINITY;
         }
@@ -329,11 +342,12 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
                                     const int* tile_row0, const int* block_table, void* out, int n_tiles, int n_heads,
                                     int n_kv_heads, int d, int dv, int chunk, int window, int max_blocks, float scale,
                                     int sink, const float* sink_values, int v_in_k, int heads_as_rows, int n_splits,
-                                    float* scratch,
+                                    float* scratch, int keep_first, float softcap,
                                     cudaStream_t stream) {
   MLL_REQUIRE(mll_local_attention_mma_supported(MLL_BF16, d, dv), "local attention (mma): head sizes %d / %d", d, dv);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "local attention (mma): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_heads <= 65535 && chunk >= 0 && window >= 0, "local attention (mma): bad tile count, chunk or window");
+  MLL_REQUIRE(keep_first >= 0 && softcap >= 0.f && (keep_first == 0 || chunk == 0), "local attention (mma): bad kept tokens or cap");
   MLL_REQUIRE(!v_in_k || dv <= d, "local attention (mma): values of %d cannot be the leading columns of keys of %d", dv, d);
   MLL_REQUIRE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || (heads_as_rows && scratch != nullptr)),
               "local attention (mma): %d context splits need single tokens and scratch memory", n_splits);
@@ -342,7 +356,8 @@ MLL_API int mll_local_attention_mma(const void* q, const void* k_cache, const vo
                       seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                       (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, d, dv,
                       scale * 1.4426950408889634f, (sink || sink_values) ? 1 : 0, sink_values, heads_as_rows ? 1 : 0, v_in_k ? d : dv, n_splits,
-                      scratch, scratch ? scratch + (size_t)n_tiles * n_heads * n_splits * dv : nullptr};
+                      scratch, scratch ? scratch + (size_t)n_tiles * n_heads * n_splits * dv : nullptr, keep_first, softcap,
+                      scale};
   if (d <= 32) return mll::dispatch_local_mma_v<32>(a, n_tiles, stream);
   if (d <= 64) return mll::dispatch_local_mma_v<64>(a, n_tiles, stream);
   if (d <= 128) return mll::dispatch_local_mma_v<128>(a, n_tiles, stream);

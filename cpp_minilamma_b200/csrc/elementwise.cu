@@ -21,7 +21,7 @@ MLL_API const char* mll_last_error() { return g_error; }
 thread_local cudaError_t mll_launch_status = cudaSuccess;
 
 // Identifies the build; the Python side checks it after loading the library.
-MLL_API int mll_abi_version() { return 32; }
+MLL_API int mll_abi_version() { return 33; }
 
 // Cache positions per page, for the Python side to check against its own constant.
 MLL_API int mll_page() { return MLL_PAGE; }
@@ -48,19 +48,19 @@ MLL_API int mll_multiprocessor_count() { return mll_sm_count(); }
 
 namespace mll {
 
-// x[t, :] = float(table[token[t], :]); the residual stream is float32.
+// x[t, :] = scale * float(table[token[t], :]); the residual stream is float32.
 template <typename TableT>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const TableT* __restrict__ table,
-                                 float* __restrict__ x, int width) {
+                                 float* __restrict__ x, int width, float scale) {
   const int t = blockIdx.x;
   const TableT* row = table + (size_t)tokens[t] * width;
   float* out = x + (size_t)t * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]) * scale;
 }
 
 // the same for a bfloat16 table whose rows are multiples of 8 elements: 16-byte loads, one per thread and pass
 __global__ void embedding_bf16_vec8_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ table,
-                                           float* __restrict__ x, int width) {
+                                           float* __restrict__ x, int width, float scale) {
   const int t = blockIdx.x;
   const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)tokens[t] * width);
   float4* out = reinterpret_cast<float4*>(x + (size_t)t * width);
@@ -69,8 +69,8 @@ __global__ void embedding_bf16_vec8_kernel(const int* __restrict__ tokens, const
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
     const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
     const float2 c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
-    out[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-    out[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+    out[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    out[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
   }
 }
 
@@ -131,9 +131,10 @@ __global__ void cast_kernel(const In* __restrict__ in, Out* __restrict__ out, si
 // out[t, i] = silu(gate) * up.  `gu` rows hold gate and up either as two halves
 // ([gate(0..I) | up(0..I)], block == 0) or interleaved in blocks of `block` columns
 // ([gate(0..b) | up(0..b) | gate(b..2b) | ...]); I is a multiple of `block` then.
+// `bias` (float32 [2 I], in the order of a row of gu, or null) is added to gate and up first.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens,
-                              int inter, int block) {
+                              int inter, int block, const float* __restrict__ bias) {
   const size_t total = (size_t)tokens * inter;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -141,13 +142,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     const int t = (int)(idx / inter), i = (int)(idx % inter);
     const T* row = gu + (size_t)t * 2 * inter;
     float g, u;
-    if (block == 0) {
-      g = to_float(row[i]);
-      u = to_float(row[inter + i]);
-    } else {
-      const int b = i / block, r = i % block;
-      g = to_float(row[(size_t)b * 2 * block + r]);
-      u = to_float(row[(size_t)b * 2 * block + block + r]);
+    const int gc = block == 0 ? i : (i / block) * 2 * block + i % block;
+    const int uc = block == 0 ? inter + i : gc + block;
+    g = to_float(row[gc]);
+    u = to_float(row[uc]);
+    if (bias) {
+      g += bias[gc];
+      u += bias[uc];
     }
     const float act = g / (1.f + expf(-g));
     out[idx] = from_float<T>(act * u);
@@ -201,7 +202,8 @@ template <>
 __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
 template <typename T>
-__global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block) {
+__global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int tokens, int inter, int block,
+                                   const float* __restrict__ bias) {
   const int groups = inter >> 3;
   const size_t total = (size_t)tokens * groups;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -214,10 +216,25 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out
     float g[8], u[8], r[8];
     Pack8<T>::load(gp, g);
     Pack8<T>::load(up, u);
+    if (bias) {
+      const float* gb = bias + (gp - row);
+      const float* ub = bias + (up - row);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        g[i] += gb[i];
+        u[i] += ub[i];
+      }
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) r[i] = silu_mul<T>(g[i], u[i]);
     Pack8<T>::store(out + (size_t)t * inter + (size_t)b * 8, r);
   }
+}
+
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float factor) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < n; idx += stride) x[idx] *= factor;
 }
 
 // x[t, i] += bias[i] (bias float32, sum in float32)
@@ -360,6 +377,17 @@ MLL_API int mll_scatter_rows(int* table, const int* staged, int n_rows, int widt
   return 0;
 }
 
+// x[i] *= factor (float32, in place)
+MLL_API int mll_scale(float* x, long long n, float factor, cudaStream_t stream) {
+  MLL_REQUIRE(n >= 0, "scale: bad size %lld", n);
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > mll_sm_count() * 16) blocks = mll_sm_count() * 16;
+  MLL_LAUNCH((mll::scale_kernel), (int)blocks, 256, 0, stream, x, (size_t)n, factor);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
 MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int width, cudaStream_t stream) {
   MLL_REQUIRE(n_rows >= 0 && width > 0, "add_bias: bad sizes rows=%d width=%d", n_rows, width);
   if (n_rows == 0) return 0;
@@ -377,17 +405,17 @@ MLL_API int mll_add_bias(void* x, const float* bias, int dtype, int n_rows, int 
 }
 
 MLL_API int mll_embedding(const int* tokens, const void* table, int table_dtype, float* x,
-                          int n_tokens, int width, cudaStream_t stream) {
+                          int n_tokens, int width, float scale, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && width > 0, "embedding: bad sizes tokens=%d width=%d", n_tokens, width);
   if (n_tokens == 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == MLL_F32)
-    MLL_LAUNCH((mll::embedding_kernel<float>), n_tokens, threads, 0, stream, tokens, (const float*)table, x, width);
+    MLL_LAUNCH((mll::embedding_kernel<float>), n_tokens, threads, 0, stream, tokens, (const float*)table, x, width, scale);
   else if (table_dtype == MLL_BF16 && width % 8 == 0 && ((uintptr_t)table % 16 == 0) && ((uintptr_t)x % 16 == 0))
     MLL_LAUNCH((mll::embedding_bf16_vec8_kernel), n_tokens, width >= 2048 ? 256 : 64, 0, stream, tokens,
-               (const __nv_bfloat16*)table, x, width);
+               (const __nv_bfloat16*)table, x, width, scale);
   else if (table_dtype == MLL_BF16)
-    MLL_LAUNCH((mll::embedding_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, tokens, (const __nv_bfloat16*)table, x, width);
+    MLL_LAUNCH((mll::embedding_kernel<__nv_bfloat16>), n_tokens, threads, 0, stream, tokens, (const __nv_bfloat16*)table, x, width, scale);
   else
     MLL_REQUIRE(false, "embedding: unknown table dtype %d", table_dtype);
   MLL_LAUNCH_CHECK();
@@ -450,7 +478,7 @@ MLL_API int mll_swiglu_rows(const void* gu, void* out, int n_tokens, int inter, 
   return 0;
 }
 
-MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int inter, int block,
+MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int inter, int block, const float* bias,
                        cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && inter > 0, "swiglu: bad sizes tokens=%d inter=%d", n_tokens, inter);
   MLL_REQUIRE(block >= 0 && (block == 0 || inter % block == 0),
@@ -464,9 +492,9 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
     if (groups > mll_sm_count() * 32) groups = mll_sm_count() * 32;
     if (dtype == MLL_F32)
       MLL_LAUNCH((mll::swiglu_vec8_kernel<float>), (int)groups, threads, 0, stream, (const float*)gu, (float*)out, n_tokens,
-                                                                       inter, block);
+                                                                       inter, block, bias);
     else if (dtype == MLL_BF16)
-      MLL_LAUNCH((mll::swiglu_vec8_kernel<__nv_bfloat16>), (int)groups, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+      MLL_LAUNCH((mll::swiglu_vec8_kernel<__nv_bfloat16>), (int)groups, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block, bias);
     else
       MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
     MLL_LAUNCH_CHECK();
@@ -475,9 +503,9 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
   long long blocks = ((long long)n_tokens * inter + threads - 1) / threads;
   if (blocks > mll_sm_count() * 32) blocks = mll_sm_count() * 32;
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::swiglu_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter, block);
+    MLL_LAUNCH((mll::swiglu_kernel<float>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, n_tokens, inter, block, bias);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::swiglu_kernel<__nv_bfloat16>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block);
+    MLL_LAUNCH((mll::swiglu_kernel<__nv_bfloat16>), (int)blocks, threads, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block, bias);
   else
     MLL_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

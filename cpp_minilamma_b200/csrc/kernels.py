@@ -14,7 +14,7 @@ import torch
 from ..cache.paged import PAGE  # cache positions per page; the library's MLL_PAGE is checked against it on load
 from .build import KernelBuildError, load_library
 
-ABI_VERSION = 32
+ABI_VERSION = 33
 MAX_TOP_K = 1024
 
 
@@ -138,8 +138,8 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 # --------------------------------------------------------------------------- #
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = float32(table[tokens[t], :]); tokens int32 [T], out float32 [T, D]."""
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = scale * float32(table[tokens[t], :]); tokens int32 [T], out float32 [T, D]."""
     _need(tokens, "embedding tokens", torch.int32, 1)
     _need(table, "embedding table", None, 2)
     _need(out, "embedding out", torch.float32, 2)
@@ -147,7 +147,13 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> N
     if out.shape[0] < n or out.shape[1] != width:
         raise KernelError(f"embedding: out {tuple(out.shape)} does not fit [{n}, {width}]")
     _check(lib().mll_embedding(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
-                               ctypes.c_int(n), ctypes.c_int(width), _stream()), "embedding")
+                               ctypes.c_int(n), ctypes.c_int(width), ctypes.c_float(scale), _stream()), "embedding")
+
+
+def scale_(x: torch.Tensor, factor: float) -> None:
+    """x *= factor (float32, in place)."""
+    _need(x, "scale x", torch.float32)
+    _check(lib().mll_scale(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(factor), _stream()), "scale")
 
 
 def embedding_pair(tokens, tok_pos, tok_seq, seq_slot, seq_qstart, seq_qlen, prev_token, table, pairs, out,
@@ -471,8 +477,9 @@ SMALL_LINEAR = "auto"  # "auto", a forced kind ("tc5", "tma", "direct"), or "non
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optional[RowNorm] = None,
-           width: int = 0) -> None:
+           width: int = 0, bias: Optional[torch.Tensor] = None) -> None:
     """out[t, i] = silu(gate) * up; gate_up [T, 2I] holds halves (block 0) or blocks of `block`.
+    `bias` (float32 [2I], in the order of gate_up's columns) is added to gate and up first, in float32.
     `row_norm` (bfloat16, I a multiple of 8): gate_up was computed from rows of `width` columns that lacked their
     norm's factor; gate and up are multiplied by it first."""
     _need(gate_up, "swiglu gate_up", None, 2)
@@ -480,6 +487,10 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optio
     tokens, inter = out.shape
     if gate_up.shape[0] != tokens or gate_up.shape[1] != 2 * inter:
         raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "swiglu bias", torch.float32, 1)
+        if bias.shape[0] != 2 * inter or row_norm is not None:
+            raise KernelError("swiglu: the bias has one value per column of gate_up (and no row factors with it)")
     if row_norm is not None:
         if gate_up.dtype != torch.bfloat16 or inter % 8 or block not in (0, 8) or width <= 0:
             raise KernelError("swiglu: rows without their norm's factor need bfloat16, I % 8 == 0 and the rows' width")
@@ -489,7 +500,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int, row_norm: Optio
                "swiglu_rows")
         return
     _check(lib().mll_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), ctypes.c_int(tokens),
-                            ctypes.c_int(inter), ctypes.c_int(block), _stream()), "swiglu")
+                            ctypes.c_int(inter), ctypes.c_int(block), _ptr(bias), _stream()), "swiglu")
 
 
 class DeltaNorm(NamedTuple):
@@ -1004,13 +1015,15 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, seed: int, requ
 # --------------------------------------------------------------------------- #
 def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, seq_slot, block_table, q_out,
                             k_cache, v_cache, n_heads: int, n_kv_heads: int, d: int, dv: int, rot: int,
-                            interleaved: bool, eps: float, q_temp=None, v_from_k: bool = False) -> None:
+                            interleaved: bool, eps: float, q_temp=None, v_from_k: bool = False,
+                            write_kv: bool = True) -> None:
     """qkv [T, ld] (q heads of d, k heads of d, v heads of dv; `v_from_k`: no v columns - the values are the keys as
     projected, before norm and rotation, and dv == d): q and k each divided by the root mean square of
     their whole projection and multiplied by `q_weight` / `k_weight` (float32; both None: no norm), the first
     `rot` dimensions of every q and k head rotated, q to `q_out` [T, Hq * d], k and v into the cache pages
     ([pages, Hk, PAGE, d] and [pages, Hk, PAGE, dv]).  `q_temp` = (coef, every): q at position p is also
-    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
+    multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).  `write_kv` False: the rows hold queries only and
+    nothing goes to the cache (a layer that reads another layer's keys and values)."""
     _need(qkv, "local attention qkv", None, 2)
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     if q_temp and every < 1:
@@ -1043,7 +1056,7 @@ def local_attention_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq,
         dtype_code(qkv.dtype), ctypes.c_int(n), ctypes.c_int(qkv.shape[1]), ctypes.c_int(n_heads),
         ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(rot), ctypes.c_int(int(interleaved)),
         ctypes.c_int(block_table.shape[1]), ctypes.c_float(eps), ctypes.c_float(coef), ctypes.c_int(every),
-        ctypes.c_int(int(v_from_k)), _stream()),
+        ctypes.c_int(int(v_from_k)), ctypes.c_int(int(write_kv)), _stream()),
         "local_attention_prepare")
 
 
@@ -1059,11 +1072,14 @@ def _check_local_caches(k_cache, v_cache, n_kv_heads: int, d: int, dv: int, v_in
 
 def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table, out, n_heads: int, n_kv_heads: int,
                     d: int, dv: int, chunk: int, window: int, scale: float, sink: bool = False,
-                    v_in_k: bool = False, sink_values: Optional[torch.Tensor] = None) -> None:
+                    v_in_k: bool = False, sink_values: Optional[torch.Tensor] = None, keep_first: int = 0,
+                    softcap: float = 0.0) -> None:
     """out [T, Hq * dv] = softmax(scale * q . k) v over the keys j <= i of the query's own chunk (j // chunk ==
     i // chunk; chunk 0: all) and window (j > i - window; 0: none); the step's own keys are in the cache already.
     `sink`: the softmax's denominator has one more term exp(0), or exp(sink_values[head]) with `sink_values` (float32
-    [Hq], not scaled).  `v_in_k`: the values are the leading dv columns of the key rows (v_cache is k_cache)."""
+    [Hq], not scaled).  `v_in_k`: the values are the leading dv columns of the key rows (v_cache is k_cache).
+    `keep_first`: with a window, keys j < keep_first stay visible.  `softcap` > 0: a score s becomes
+    softcap * tanh(s / softcap) after the scale."""
     _need(q, "local attention q", None, 2)
     _check_sink_values(sink_values, n_heads)
     _need(out, "local attention out", q.dtype, 2)
@@ -1078,7 +1094,7 @@ def local_attention(q, k_cache, v_cache, tok_pos, tok_seq, seq_slot, block_table
         _ptr(out), dtype_code(q.dtype), ctypes.c_int(n), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk), ctypes.c_int(window),
         ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)), _ptr(sink_values),
-        ctypes.c_int(int(v_in_k)), _stream()), "local_attention")
+        ctypes.c_int(int(v_in_k)), ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()), "local_attention")
 
 
 USE_TENSOR_CORE_LOCAL = True  # tests switch it off to reach the general kernel in bfloat16 prompt steps
@@ -1092,7 +1108,7 @@ def local_attention_mma_supported(dtype: torch.dtype, d: int, dv: int) -> bool:
 def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                           block_table, out, n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int,
                           scale: float, sink: bool = False, v_in_k: bool = False,
-                          sink_values: Optional[torch.Tensor] = None) -> None:
+                          sink_values: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: float = 0.0) -> None:
     """`local_attention` for prompt steps in bfloat16 on tensor cores: the work is a list of tiles of up to
     PREFILL_TILE query rows, (sequence, first row among the sequence's new tokens)."""
     _need(q, "local attention q", torch.bfloat16, 2)
@@ -1112,14 +1128,16 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         _ptr(tile_seq), _ptr(tile_row0), _ptr(block_table), _ptr(out), ctypes.c_int(tile_seq.shape[0]),
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
-        _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None), _stream()),
+        _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None),
+        ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
         "local_attention_mma")
 
 
 def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, block_table, out, n_seqs: int,
                           n_heads: int, n_kv_heads: int, d: int, dv: int, chunk: int, window: int, scale: float,
                           sink: bool = False, v_in_k: bool = False, n_splits: int = 1,
-                          scratch: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None) -> None:
+                          scratch: Optional[torch.Tensor] = None, sink_values: Optional[torch.Tensor] = None,
+                          keep_first: int = 0, softcap: float = 0.0) -> None:
     """`local_attention` for steps in which every sequence brings one token, bfloat16, on tensor cores: a block per
     (sequence, kv head) whose rows are the query heads of that kv head's group.  `n_splits` > 1: that many blocks
     along every context and a merge; `scratch` float32 of `local_attention_heads_scratch` floats."""
@@ -1140,7 +1158,8 @@ def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(chunk),
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
         _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(1), ctypes.c_int(n_splits),
-        _ptr(scratch if n_splits > 1 else None), _stream()), "local_attention_heads", kernels=2 if n_splits > 1 else 1)
+        _ptr(scratch if n_splits > 1 else None), ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
+        "local_attention_heads", kernels=2 if n_splits > 1 else 1)
 
 
 def local_attention_heads_scratch(n_seqs: int, n_heads: int, dv: int, n_splits: int) -> int:
@@ -1211,27 +1230,33 @@ def delta_prepare(proj, rate, conv_w, conv_state, a_log, dt_bias, tok_seq, seq_s
         _stream()), "delta_prepare")
 
 
-def conv_state_update(proj, conv_state, seq_slot, seq_qstart, seq_qlen, n_seqs: int, channels: int, taps: int) -> None:
-    """conv_state[slot] <- the last taps - 1 rows of (conv_state[slot], this step's rows of proj[:, :channels])."""
+def conv_state_update(proj, conv_state, seq_slot, seq_qstart, seq_qlen, n_seqs: int, channels: int, taps: int,
+                      first_column: int = 0) -> None:
+    """conv_state[slot] <- the last taps - 1 rows of (conv_state[slot], this step's rows of
+    proj[:, first_column:first_column + channels])."""
     _need(proj, "conv state proj", None, 2)
     _need(conv_state, "conv state", torch.float32, 3)
     if tuple(conv_state.shape[1:]) != (max(taps - 1, 0), channels):
         raise KernelError(f"conv state update: state {tuple(conv_state.shape)} for {channels} channels of {taps} taps")
     _check(lib().mll_conv_state_update(
-        _ptr(proj), dtype_code(proj.dtype), ctypes.c_int(proj.shape[1]), _ptr(conv_state), _ptr(seq_slot),
+        _ptr(proj), dtype_code(proj.dtype), ctypes.c_int(first_column), ctypes.c_int(proj.shape[1]), _ptr(conv_state),
+        _ptr(seq_slot),
         _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(channels), ctypes.c_int(taps), _stream()),
         "conv_state_update")
 
 
 def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, seq_qlen, n_seqs: int, n_heads: int,
-               n_kv_heads: int, d: int, dv: int) -> None:
+               n_kv_heads: int, d: int, dv: int, token_decay: Optional[torch.Tensor] = None) -> None:
     """The recurrence S <- decay S + k u^T, o = S^T q over each sequence's tokens of the step, from and to
     state [slots, H, d, dv] (float32).  With g [T, H * d] and beta [T, H]: the gated delta rule
-    (u = beta (v - S^T k) after the decay); with g alone: a decay per key channel and u = v; else head_decay
-    float32 [H] and u = v."""
+    (u = beta (v - S^T k) after the decay); with g alone: a decay per key channel and u = v; with `token_decay`
+    float32 [T, H]: one decay per token and head and u = v; else head_decay float32 [H] and u = v."""
     n = q.shape[0]
     delta = g is not None and beta is not None
     channel = g is not None and beta is None
+    per_token = token_decay is not None
+    if per_token and (g is not None or beta is not None or head_decay is not None):
+        raise KernelError("state scan: a decay per token and head stands alone")
     for name, t, width in (("q", q, n_kv_heads * d), ("k", k, n_kv_heads * d), ("v", v, n_heads * dv),
                            ("out", out, n_heads * dv)):
         _need(t, f"state scan {name}", torch.float32, 2)
@@ -1249,6 +1274,11 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
         _need(g, "state scan g", torch.float32, 2)
         if tuple(g.shape) != (n, n_heads * d):
             raise KernelError("state scan: g of the wrong size")
+    elif per_token:
+        _need(token_decay, "state scan token decay", torch.float32, 2)
+        if tuple(token_decay.shape) != (n, n_heads):
+            raise KernelError("state scan: one decay per token and head is needed")
+        beta = token_decay  # it travels where the delta rule's beta does
     else:
         _need(head_decay, "state scan decay", torch.float32, 1)
         if head_decay.shape[0] != n_heads:
@@ -1256,8 +1286,65 @@ def state_scan(q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, s
     _check(lib().mll_state_scan(
         _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(head_decay), _ptr(state), _ptr(out), _ptr(seq_slot),
         _ptr(seq_qstart), _ptr(seq_qlen), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
-        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(1 if delta else (2 if channel else 0)), _stream()),
-        "state_scan (delta rule)" if delta else ("state_scan (channel decay)" if channel else "state_scan (retention)"))
+        ctypes.c_int(d), ctypes.c_int(dv), ctypes.c_int(1 if delta else (2 if channel else (3 if per_token else 0))),
+        _stream()),
+        "state_scan (delta rule)" if delta else ("state_scan (channel decay)" if channel else
+                                                 ("state_scan (token decay)" if per_token else "state_scan (retention)")))
+
+
+def ssd_prepare(proj, conv_w, conv_b, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, u, xs, decay,
+                n_heads: int, n_groups: int, d: int, dv: int, taps: int) -> None:
+    """The inputs of a state-space layer from the projection of a step: a row of proj [T, ld] holds z (H dv), x (H dv),
+    B (G d), C (G d) and dt (H).  x, B and C pass a causal convolution over time (conv_w float32 [C, taps], conv_b
+    [C], the inputs before the step from conv_state float32 [slots, taps - 1, C]) and silu; dt = softplus(dt +
+    dt_bias).  Float32 outputs: q = C and k = B [T, G d], xs = x and u = dt x [T, H dv], decay = exp(-exp(a_log) dt)
+    [T, H]."""
+    _need(proj, "ssd proj", None, 2)
+    n = proj.shape[0]
+    inner, gn = n_heads * dv, n_groups * d
+    C = inner + 2 * gn
+    for name, t, shape in (("conv weights", conv_w, (C, taps)), ("conv bias", conv_b, (C,)), ("A_log", a_log, (n_heads,)),
+                           ("dt_bias", dt_bias, (n_heads,)), ("q", q, (n, gn)), ("k", k, (n, gn)), ("u", u, (n, inner)),
+                           ("xs", xs, (n, inner)), ("decay", decay, (n, n_heads))):
+        _need(t, f"ssd {name}", torch.float32)
+        if tuple(t.shape) != shape:
+            raise KernelError(f"ssd prepare: {name} {tuple(t.shape)}, expected {shape}")
+    _need(conv_state, "ssd conv state", torch.float32, 3)
+    if tuple(conv_state.shape[1:]) != (max(taps - 1, 0), C):
+        raise KernelError(f"ssd prepare: conv state {tuple(conv_state.shape)} for {C} channels of {taps} taps")
+    if proj.shape[1] < 2 * inner + 2 * gn + n_heads:
+        raise KernelError(f"ssd prepare: rows of {proj.shape[1]} columns are too short")
+    _check(lib().mll_ssd_prepare(
+        _ptr(proj), _ptr(conv_w), _ptr(conv_b), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(tok_seq),
+        _ptr(seq_slot), _ptr(seq_qstart), _ptr(q), _ptr(k), _ptr(u), _ptr(xs), _ptr(decay), dtype_code(proj.dtype),
+        ctypes.c_int(n), ctypes.c_int(proj.shape[1]), ctypes.c_int(n_heads), ctypes.c_int(n_groups), ctypes.c_int(d),
+        ctypes.c_int(dv), ctypes.c_int(taps), _stream()), "ssd_prepare")
+
+
+def gated_group_norm(o, xs, skip, gate, weight, out, dv: int, parts: int, eps: float) -> None:
+    """out = y / sqrt(mean(y^2) + eps) * weight over each of `parts` equal pieces of a row, with
+    y = (o + skip[head] * xs) * silu(gate[:, :width]); o, xs float32 [T, width], skip float32 [width / dv] (both None:
+    no skip), gate [T, >= width] and out [T, width] in the run's dtype, weight float32 [width]."""
+    _need(o, "gated group norm o", torch.float32, 2)
+    n, width = o.shape
+    _need(gate, "gated group norm gate", None, 2)
+    _need(out, "gated group norm out", gate.dtype, 2)
+    _need(weight, "gated group norm weight", torch.float32, 1)
+    if (xs is None) != (skip is None):
+        raise KernelError("gated group norm: a skip needs its input and its factors")
+    if xs is not None:
+        _need(xs, "gated group norm xs", torch.float32, 2)
+        _need(skip, "gated group norm skip", torch.float32, 1)
+        if tuple(xs.shape) != (n, width) or skip.shape[0] * dv != width:
+            raise KernelError("gated group norm: the skip's input or factors of the wrong size")
+    if tuple(out.shape) != (n, width) or weight.shape[0] != width or gate.shape[0] != n or gate.shape[1] < width:
+        raise KernelError(f"gated group norm: o {tuple(o.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}")
+    if parts < 1 or width % parts:
+        raise KernelError(f"gated group norm: {width} columns in {parts} parts")
+    _check(lib().mll_gated_group_norm(
+        _ptr(o), _ptr(xs), _ptr(skip), _ptr(gate), dtype_code(gate.dtype), ctypes.c_int(gate.shape[1]), _ptr(weight),
+        _ptr(out), dtype_code(out.dtype), ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(dv), ctypes.c_int(parts),
+        ctypes.c_float(eps), _stream()), "gated_group_norm")
 
 
 def channel_decay_prepare(proj, rate, bias, q, k, v, g, n_heads: int, d: int, dv: int, q_scale: float, tau: float) -> None:
@@ -1381,12 +1468,14 @@ def moe_max_tiles(n_pairs: int, n_experts: int, rows: int) -> int:
 
 
 def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tensor] = None, all_scores: bool = False,
-              scale: float = 1.0, gate_out: Optional[torch.Tensor] = None) -> None:
+              scale: float = 1.0, gate_out: Optional[torch.Tensor] = None, groups=None) -> None:
     """chosen [T, top] (int32) = the experts with the largest z = w h + bias (float32; ties: the lower index),
     weight [T, top] (float32) = softmax over the chosen logits.  `logits`: float32 [T, E] = h w^T when the caller
     has formed the product already (a library product over many tokens).
     `all_scores`: s = softmax(w h) over every expert, the choice goes by s + bias, weight = the chosen s over their
-    sum (+ 1e-20), times `scale`.  `gate_out` (float32 [T]): w (and logits) have one more row behind the experts';
+    sum (+ 1e-20), times `scale`.  `groups` = (count, kept): s = sigmoid(w h); the experts form `count` equal groups
+    of neighbours, a group scores the sum of its two largest s, only experts of the `kept` best groups can be chosen;
+    weight as with `all_scores`.  `gate_out` (float32 [T]): w (and logits) have one more row behind the experts';
     the sigmoid of its product with the token goes there."""
     _need(h, "moe route h", None, 2)
     _need(w, "moe route weight", torch.float32, 2)
@@ -1411,7 +1500,9 @@ def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tenso
             raise KernelError(f"moe route: logits {tuple(logits.shape)}, expected {(n, rows)}")
     _check(lib().mll_moe_route(_ptr(h), _ptr(w), _ptr(bias), _ptr(logits), _ptr(chosen), _ptr(weight), dtype_code(h.dtype),
                                ctypes.c_int(n), ctypes.c_int(width), ctypes.c_int(experts), ctypes.c_int(top),
-                               ctypes.c_int(int(all_scores)), ctypes.c_float(scale), _ptr(gate_out), _stream()),
+                               ctypes.c_int(2 if groups else int(all_scores)), ctypes.c_float(scale), _ptr(gate_out),
+                               ctypes.c_int(int(groups[0]) if groups else 0), ctypes.c_int(int(groups[1]) if groups else 0),
+                               _stream()),
            "moe_route")
 
 

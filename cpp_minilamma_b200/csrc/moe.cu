@@ -29,10 +29,14 @@ namespace mll {
 // all_scores 1: softmax over every expert; the choice goes by score + bias, the weights are the chosen scores over
 // their sum, times `scale`.  gate_out: the router's matrix has one more row behind the experts'; the sigmoid of its
 // product with the token goes to gate_out[t] (a per-token gate of another part that reads the same rows).
+// all_scores 2: scores = sigmoid of every logit; the experts form `groups` equal groups of neighbours, a group scores
+// the sum of its two largest scores (its one score if it has one expert), and only experts of the `groups_kept` best
+// groups can be chosen (ties: the lower group); the weights are the chosen scores over their sum, times `scale`.
 struct RouteForm {
   int all_scores;
   float scale;
   float* gate_out;
+  int groups, groups_kept;
 };
 
 template <typename T>
@@ -85,9 +89,43 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
   if (warp != 0) return;
   if (form.gate_out && lane == 0) form.gate_out[t] = 1.f / (1.f + expf(-z[n_experts]));
   if (form.all_scores) {
-    // scores = softmax over every expert; the choice goes by score + correction, the weights by the scores alone:
-    // weight_j = score_j / (sum of the chosen scores + 1e-20) * scale
+    // scores over every expert; the choice goes by score + correction (or by score inside the kept groups), the
+    // weights by the scores alone:  weight_j = score_j / (sum of the chosen scores + 1e-20) * scale
     float* choice = z + n_rows;  // [n_experts]
+    if (form.all_scores == 2) {
+      float* group_score = choice + n_experts;  // [groups]
+      const int per = n_experts / form.groups;
+      for (int e = lane; e < n_experts; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+      __syncwarp();
+      for (int g = lane; g < form.groups; g += 32) {
+        float a = -INFINITY, b = -INFINITY;  // the group's two largest scores
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = z[e];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        group_score[g] = per > 1 ? a + b : a;
+      }
+      for (int e = lane; e < n_experts; e += 32) choice[e] = -INFINITY;
+      __syncwarp();
+      for (int j = 0; j < form.groups_kept; ++j) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int g = lane; g < form.groups; g += 32) {
+          const float v = group_score[g];
+          if (v > best || (v == best && g < at)) { best = v; at = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+          if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= form.groups) break;  // nothing comparable was left
+        for (int e = at * per + lane; e < (at + 1) * per; e += 32) choice[e] = z[e];
+        if (lane == 0) group_score[at] = -INFINITY;
+        __syncwarp();
+      }
+    } else {
     float top_z = -INFINITY;
     for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, z[e]);
     top_z = warp_max(top_z);
@@ -98,6 +136,7 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
       const float sc = expf(z[e] - top_z) / denom;
       z[e] = sc;
       choice[e] = sc + (bias ? bias[e] : 0.f);
+    }
     }
     __syncwarp();
     float chosen_sum = 0.f;
@@ -329,13 +368,22 @@ MLL_API int mll_moe_simt_rows() { return MOE_SIMT_BM; }
 // chosen: int32 [n_tokens, top]; weight: float32 [n_tokens, top].
 MLL_API int mll_moe_route(const void* h, const float* w, const float* bias, const float* logits, int* chosen,
                           float* weight, int dtype, int n_tokens, int width, int n_experts, int top, int all_scores,
-                          float scale, float* gate_out, cudaStream_t stream) {
+                          float scale, float* gate_out, int groups, int groups_kept, cudaStream_t stream) {
   MLL_REQUIRE(n_tokens >= 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts && top <= 32,
               "moe route: bad sizes tokens=%d width=%d experts=%d top=%d", n_tokens, width, n_experts, top);
   MLL_REQUIRE(n_experts <= 2048, "moe route: %d experts (at most 2048)", n_experts);
   if (n_tokens == 0) return 0;
-  const size_t smem = (size_t)(2 * n_experts + 1) * sizeof(float);
-  const mll::RouteForm form{all_scores ? 1 : 0, scale, gate_out};
+  MLL_REQUIRE(all_scores >= 0 && all_scores <= 2, "moe route: unknown scoring %d", all_scores);
+  if (all_scores == 2) {
+    MLL_REQUIRE(groups >= 1 && n_experts % groups == 0 && groups_kept >= 1 && groups_kept <= groups,
+                "moe route: %d experts in %d groups of which %d are kept", n_experts, groups, groups_kept);
+    MLL_REQUIRE(top <= groups_kept * (n_experts / groups), "moe route: top %d of %d experts in the kept groups", top,
+                groups_kept * (n_experts / groups));
+  } else {
+    groups = groups_kept = 0;
+  }
+  const size_t smem = (size_t)(2 * n_experts + 1 + groups) * sizeof(float);
+  const mll::RouteForm form{all_scores, scale, gate_out, groups, groups_kept};
   if (dtype == MLL_F32)
     MLL_LAUNCH((mll::moe_route_kernel<float>), n_tokens, 512, smem, stream, (const float*)h, w, bias, logits, chosen,
                weight, n_tokens, width, n_experts, top, form);

@@ -15,11 +15,14 @@
 //                         q / sqrt(d), beta = sigmoid, g = exp(-exp(A) softplus(x + bias))
 //   * channel_decay_prepare  q * q_scale, k, v to float32 and g = sigmoid(z + bias)^(1 / tau) per key channel,
 //                         formed as exp(log_sigmoid(z + bias) / tau) in float32
+//   * ssd_prepare         a state-space layer's inputs: short causal convolution with bias + silu on (x, B, C),
+//                         dt = softplus(dt + bias), decay = exp(-exp(A) dt) per token and head, u = dt x
 //   * conv_state_update   the last taps - 1 convolution inputs of every sequence, kept for the next step
 //   * state_scan          the recurrence: a column of S lives in the registers of R lanes (ROWS rows each);
 //                         per token every product is local to the column, two shuffles-reductions over the
 //                         R lanes give S^T k and S^T q
 //   * head_norm_gate      o / rms(o) per head (* weight) * silu or sigmoid of a gate, to the activation dtype
+//   * gated_group_norm    (o + skip_h x) * silu(z), then / rms over each of a few equal parts of the row, * weight
 #include "common.cuh"
 
 namespace mll {
@@ -177,13 +180,77 @@ __global__ void __launch_bounds__(256) channel_decay_prepare_kernel(ChannelDecay
   for (int i = threadIdx.x; i < nv; i += blockDim.x) a.v[(size_t)t * nv + i] = to_float(row[2 * n + i]);
 }
 
+// A state-space layer's inputs.  A row of proj is [z (H dv) | x (H dv) | B (G d) | C (G d) | dt (H)]; x, B and C
+// pass a causal convolution over time (taps per channel, the last one meets the current token; the inputs before a
+// step's first token come from the sequence's state) with a bias and silu.
+//   dt_h = softplus(dt_h + dt_bias_h)   decay[t, h] = exp(-exp(A_h) dt_h)   u[t, h, :] = dt_h x[t, h, :]
+//   k = B, q = C (per group), xs = x after the convolution (for the skip).  All float32.
+struct SsdPrepArgs {
+  const void* proj;        // [T, ld]
+  const float* conv_w;     // [C, taps], C = H dv + 2 G d
+  const float* conv_b;     // [C]
+  const float* conv_state; // [slots, taps - 1, C]
+  const float* a_log;      // [H]
+  const float* dt_bias;    // [H]
+  const int* tok_seq;
+  const int* seq_slot;
+  const int* seq_qstart;
+  float* q;                // [T, G, d]
+  float* k;                // [T, G, d]
+  float* u;                // [T, H, dv]
+  float* xs;               // [T, H, dv]
+  float* decay;            // [T, H]
+  int ld, n_heads, n_groups, d, dv, taps;
+};
+
+// grid (tokens), 256 threads; dynamic shared memory: H floats (dt per head).
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_prepare_kernel(SsdPrepArgs a) {
+  extern __shared__ float dt_s[];
+  const int t = blockIdx.x;
+  const int H = a.n_heads, G = a.n_groups, d = a.d, dv = a.dv, taps = a.taps;
+  const int inner = H * dv, gn = G * d, C = inner + 2 * gn;
+  const T* proj = (const T*)a.proj;
+  const T* row = proj + (size_t)t * a.ld;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float dt = softplus_f(to_float(row[inner + C + h]) + a.dt_bias[h]);
+    dt_s[h] = dt;
+    a.decay[(size_t)t * H + h] = expf(-expf(a.a_log[h]) * dt);
+  }
+  __syncthreads();
+  const int seq = a.tok_seq[t];
+  const int local = t - a.seq_qstart[seq];  // index among this step's tokens of the sequence
+  const float* state = a.conv_state + (size_t)a.seq_slot[seq] * (taps - 1) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float y = a.conv_b[c];
+    for (int back = 0; back < taps; ++back) {  // the input `back` tokens ago meets tap taps - 1 - back
+      float x;
+      if (back <= local)
+        x = to_float(proj[(size_t)(t - back) * a.ld + inner + c]);
+      else
+        x = state[(size_t)(local - back + taps - 1) * C + c];
+      y = fmaf(a.conv_w[(size_t)c * taps + (taps - 1 - back)], x, y);
+    }
+    y = silu_f(y);
+    if (c < inner) {
+      a.xs[(size_t)t * inner + c] = y;
+      a.u[(size_t)t * inner + c] = dt_s[c / dv] * y;
+    } else if (c < inner + gn) {
+      a.k[(size_t)t * gn + (c - inner)] = y;
+    } else {
+      a.q[(size_t)t * gn + (c - inner - gn)] = y;
+    }
+  }
+}
+
 // grid (ceil(C / 128), sequences): new state = the last taps - 1 of (old state, this step's inputs)
 template <typename T>
-__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, float* __restrict__ conv_state,
+__global__ void conv_state_update_kernel(const T* __restrict__ proj_rows, int col0, int ld, float* __restrict__ conv_state,
                                          const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                                          const int* __restrict__ seq_qlen, int C, int taps) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  const T* proj = proj_rows + col0;  // the convolution's channels begin at column col0 of a row
   const int seq = blockIdx.y;
   const int n = seq_qlen[seq], row0 = seq_qstart[seq], keep = taps - 1;
   float* state = conv_state + (size_t)seq_slot[seq] * keep * C;
@@ -200,8 +267,8 @@ struct ScanArgs {
   const float* q;           // [T, G, d]
   const float* k;           // [T, G, d]
   const float* v;           // [T, H, dv]
-  const float* g;           // [T, H, d] (DELTA) or null
-  const float* beta;        // [T, H] (DELTA) or null
+  const float* g;           // [T, H, d] (a decay per key channel) or null
+  const float* beta;        // [T, H]: the delta rule's beta, or (MODE 3) one decay per token and head; else null
   const float* head_decay;  // [H] (not DELTA)
   float* state;             // [slots, H, d, dv]
   float* out;               // [T, H, dv]
@@ -223,11 +290,13 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 // are staged as 0, so their S stays 0 and adds nothing.  The tokens' q, k, g, v and beta arrive in shared memory
 // `tok_stage` tokens at a time through a two-stage ring of asynchronous copies, so that the next tokens load
 // while these are worked on and the chain from token to token is arithmetic only.
-// MODE 0: one decay per head; 1: the delta rule with a decay per key channel; 2: a decay per key channel, u = v.
+// MODE 0: one decay per head; 1: the delta rule with a decay per key channel; 2: a decay per key channel, u = v;
+// 3: one decay per token and head (it travels where the delta rule's beta does), u = v.
 template <int ROWS, int R, int MODE, int THREADS>
 __global__ void __launch_bounds__(THREADS) state_scan_kernel(ScanArgs a) {
   constexpr bool DELTA = MODE == 1;    // beta and the correction by S^T k
-  constexpr bool CHANNEL = MODE != 0;  // g per key channel travels with q and k
+  constexpr bool CHANNEL = MODE == 1 || MODE == 2;  // g per key channel travels with q and k
+  constexpr bool TOKEN_DECAY = MODE == 3;
   extern __shared__ __align__(16) float stage[];
   constexpr int DP = ROWS * R;          // padded number of rows
   constexpr int CPW = 32 / R;           // columns per warp
@@ -290,10 +359,10 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(ScanArgs a) {
       const int tt = i / CPB, c = i % CPB;
       if (col0 + c < dv) cp_async4(v_s + i, a.v + ((size_t)(row0 + t0 + tt) * H + h) * dv + col0 + c);
     }
-    if (DELTA)
+    if (DELTA || TOKEN_DECAY)
       for (int i = tid; i < nt; i += THREADS) cp_async4(b_s + i, a.beta + (size_t)(row0 + t0 + i) * H + h);
   };
-  const float decay = CHANNEL ? 1.f : a.head_decay[h];
+  const float decay = (CHANNEL || TOKEN_DECAY) ? 1.f : a.head_decay[h];
   load(0, 0);
   cp_async_commit();
   for (int t0 = 0, it = 0; t0 < n_tok; t0 += TS, ++it) {
@@ -349,6 +418,7 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(ScanArgs a) {
         for (int i = 0; i < ROWS; ++i) {
           if (MODE == 1) s[i] = fmaf(kv[i], u, s[i]);
           else if (MODE == 2) s[i] = fmaf(gv[i], s[i], kv[i] * u);
+          else if (MODE == 3) s[i] = fmaf(b_s[tj], s[i], kv[i] * u);
           else s[i] = fmaf(decay, s[i], kv[i] * u);
           o4[i & 3] = fmaf(s[i], qv[i], o4[i & 3]);
         }
@@ -378,7 +448,7 @@ int launch_scan(const ScanArgs& args, int n_seqs, cudaStream_t stream) {
   ScanArgs a = args;
   constexpr int DP = ROWS * R, CPB = (32 / R) * (THREADS / 32);
   a.tok_stage = DP <= 128 ? 16 : (DP <= 256 ? 8 : (DP <= 512 ? 4 : 2));
-  const size_t smem = (size_t)2 * ((a.tok_stage * DP * (MODE ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
+  const size_t smem = (size_t)2 * ((a.tok_stage * DP * ((MODE == 1 || MODE == 2) ? 3 : 2) + a.tok_stage * CPB + a.tok_stage + 3) & ~3) * sizeof(float);
   const dim3 grid((a.dv + CPB - 1) / CPB, a.n_heads, n_seqs);
   if (smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(state_scan_kernel<ROWS, R, MODE, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -450,7 +520,82 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __rest
   }
 }
 
+// grid (tokens, parts), 256 threads: a row of o [H dv] in `parts` equal pieces, each normalised by its own root mean
+// square after the skip and the gate:   y = (o + skip[h] xs) * silu(z);   out = y / sqrt(mean_part(y^2) + eps) * weight
+template <typename T, typename GateT>
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ o, const float* __restrict__ xs,
+                                                               const float* __restrict__ skip,
+                                                               const GateT* __restrict__ gate, int gate_ld,
+                                                               const float* __restrict__ weight, T* __restrict__ out,
+                                                               int width, int dv, int parts, float eps) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, part = blockIdx.y;
+  const int n = width / parts, c0 = part * n;
+  const float* orow = o + (size_t)t * width + c0;
+  const float* xrow = xs ? xs + (size_t)t * width + c0 : nullptr;
+  const GateT* grow = gate + (size_t)t * gate_ld + c0;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    float y = orow[e];
+    if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);
+    y *= silu_f(to_float(grow[e]));
+    ss += y * y;
+  }
+  ss = block_sum(ss, scratch);
+  const float f = 1.f / sqrtf(ss / (float)n + eps);
+  T* dst = out + (size_t)t * width + c0;
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    float y = orow[e];
+    if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);
+    y *= silu_f(to_float(grow[e]));
+    dst[e] = from_float<T>(y * f * weight[c0 + e]);
+  }
+}
+
 }  // namespace mll
+
+MLL_API int mll_ssd_prepare(const void* proj, const float* conv_w, const float* conv_b, const float* conv_state,
+                            const float* a_log, const float* dt_bias, const int* tok_seq, const int* seq_slot,
+                            const int* seq_qstart, float* q, float* k, float* u, float* xs, float* decay, int dtype,
+                            int n_tokens, int ld, int n_heads, int n_groups, int d, int dv, int taps,
+                            cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && n_heads > 0 && n_groups > 0 && n_heads % n_groups == 0, "ssd prepare: bad head counts");
+  MLL_REQUIRE(d > 0 && dv > 0 && taps >= 1, "ssd prepare: bad sizes");
+  MLL_REQUIRE(ld >= 2 * n_heads * dv + 2 * n_groups * d + n_heads, "ssd prepare: row stride %d too short", ld);
+  MLL_REQUIRE(n_heads <= 8192, "ssd prepare: %d heads (at most 8192)", n_heads);
+  if (n_tokens == 0) return 0;
+  mll::SsdPrepArgs a{proj, conv_w, conv_b, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, u, xs, decay,
+                     ld, n_heads, n_groups, d, dv, taps};
+  const size_t smem = (size_t)n_heads * sizeof(float);
+  if (dtype == MLL_F32)
+    MLL_LAUNCH((mll::ssd_prepare_kernel<float>), n_tokens, 256, smem, stream, a);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::ssd_prepare_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, a);
+  else
+    MLL_REQUIRE(false, "ssd prepare: unknown dtype %d", dtype);
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
+
+MLL_API int mll_gated_group_norm(const float* o, const float* xs, const float* skip, const void* gate, int gate_dtype,
+                                 int gate_ld, const float* weight, void* out, int out_dtype, int n_tokens, int width,
+                                 int dv, int parts, float eps, cudaStream_t stream) {
+  MLL_REQUIRE(n_tokens >= 0 && width > 0 && dv > 0 && parts > 0 && width % parts == 0 && gate_ld >= width,
+              "gated group norm: bad sizes width=%d parts=%d", width, parts);
+  MLL_REQUIRE((xs == nullptr) == (skip == nullptr), "gated group norm: a skip needs its input and its factors");
+  MLL_REQUIRE(parts <= 65535, "gated group norm: too many parts for one launch");
+  if (n_tokens == 0) return 0;
+  const dim3 grid(n_tokens, parts);
+#define MLL_GGN(T, GT)                                                                                             \
+  MLL_LAUNCH((mll::gated_group_norm_kernel<T, GT>), grid, 256, 0, stream, o, xs, skip, (const GT*)gate, gate_ld, \
+             weight, (T*)out, width, dv, parts, eps)
+  if (out_dtype == MLL_F32 && gate_dtype == MLL_F32) MLL_GGN(float, float);
+  else if (out_dtype == MLL_BF16 && gate_dtype == MLL_BF16) MLL_GGN(__nv_bfloat16, __nv_bfloat16);
+  else MLL_REQUIRE(false, "gated group norm: dtypes %d / %d", out_dtype, gate_dtype);
+#undef MLL_GGN
+  MLL_LAUNCH_CHECK();
+  return 0;
+}
 
 MLL_API int mll_retention_prepare(const void* proj, const float* cos_table, const float* sin_table, const int* tok_pos,
                                   float* q, float* k, float* v, int dtype, int n_tokens, int ld, int n_heads, int d,
@@ -514,19 +659,19 @@ MLL_API int mll_channel_decay_prepare(const void* proj, const float* rate, const
   return 0;
 }
 
-MLL_API int mll_conv_state_update(const void* proj, int dtype, int ld, float* conv_state, const int* seq_slot,
+MLL_API int mll_conv_state_update(const void* proj, int dtype, int col0, int ld, float* conv_state, const int* seq_slot,
                                   const int* seq_qstart, const int* seq_qlen, int n_seqs, int channels, int taps,
                                   cudaStream_t stream) {
-  MLL_REQUIRE(n_seqs >= 0 && channels > 0 && taps >= 1 && ld >= channels, "conv state update: bad sizes");
+  MLL_REQUIRE(n_seqs >= 0 && channels > 0 && taps >= 1 && col0 >= 0 && ld >= col0 + channels, "conv state update: bad sizes");
   if (n_seqs == 0 || taps == 1) return 0;
   MLL_REQUIRE(n_seqs <= 65535, "conv state update: too many sequences for one launch");
   const dim3 grid((channels + 127) / 128, n_seqs);
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::conv_state_update_kernel<float>), grid, 128, 0, stream, (const float*)proj, ld, conv_state,
-               seq_slot, seq_qstart, seq_qlen, channels, taps);
-  else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::conv_state_update_kernel<__nv_bfloat16>), grid, 128, 0, stream, (const __nv_bfloat16*)proj, ld,
+    MLL_LAUNCH((mll::conv_state_update_kernel<float>), grid, 128, 0, stream, (const float*)proj, col0, ld,
                conv_state, seq_slot, seq_qstart, seq_qlen, channels, taps);
+  else if (dtype == MLL_BF16)
+    MLL_LAUNCH((mll::conv_state_update_kernel<__nv_bfloat16>), grid, 128, 0, stream, (const __nv_bfloat16*)proj,
+               col0, ld, conv_state, seq_slot, seq_qstart, seq_qlen, channels, taps);
   else
     MLL_REQUIRE(false, "conv state update: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();
@@ -534,7 +679,7 @@ MLL_API int mll_conv_state_update(const void* proj, int dtype, int ld, float* co
 }
 
 // mode 1: the gated delta rule (g, beta given); 2: a decay per key channel without the delta rule (g given);
-// 0: one decay per head (head_decay given).
+// 0: one decay per head (head_decay given); 3: one decay per token and head (beta [T, H] holds it).
 MLL_API int mll_state_scan(const float* q, const float* k, const float* v, const float* g, const float* beta,
                            const float* head_decay, float* state, float* out, const int* seq_slot,
                            const int* seq_qstart, const int* seq_qlen, int n_seqs, int n_heads, int n_kv_heads, int d,
@@ -542,13 +687,14 @@ MLL_API int mll_state_scan(const float* q, const float* k, const float* v, const
   MLL_REQUIRE(n_seqs >= 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "state scan: bad head counts");
   MLL_REQUIRE(d > 0 && d <= 1024 && dv > 0, "state scan: head sizes %d / %d (keys at most 1024)", d, dv);
   MLL_REQUIRE(n_heads <= 65535 && n_seqs <= 65535, "state scan: too many heads or sequences for one launch");
-  MLL_REQUIRE(mode >= 0 && mode <= 2, "state scan: unknown mode %d", mode);
-  MLL_REQUIRE(mode == 1 ? (g && beta) : (mode == 2 ? g != nullptr : head_decay != nullptr),
+  MLL_REQUIRE(mode >= 0 && mode <= 3, "state scan: unknown mode %d", mode);
+  MLL_REQUIRE(mode == 1 ? (g && beta) : (mode == 2 ? g != nullptr : (mode == 3 ? beta != nullptr : head_decay != nullptr)),
               "state scan: the decay's inputs are missing");
   if (n_seqs == 0) return 0;
   mll::ScanArgs a{q, k, v, g, beta, head_decay, state, out, seq_slot, seq_qstart, seq_qlen, n_heads, n_kv_heads, d, dv, 0};
   if (mode == 1) return mll::dispatch_scan<1>(a, n_seqs, stream);
   if (mode == 2) return mll::dispatch_scan<2>(a, n_seqs, stream);
+  if (mode == 3) return mll::dispatch_scan<3>(a, n_seqs, stream);
   return mll::dispatch_scan<0>(a, n_seqs, stream);
 }
 

@@ -1,2 +1,2 @@
 """Architectures.  Importing the package registers them by their `architectures` name."""
-from . import kupirax, llama, malulorn, sopanex  # noqa: F401
+from . import badolix, kupirax, llama, malulorn, sopanex  # noqa: F401

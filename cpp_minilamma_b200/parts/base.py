@@ -100,13 +100,15 @@ class KVNeed:
     means only the last `window` positions are ever read.  `v_head_dim` > 0: the values' head size
     where it differs from the keys' (value pages are then [n_kv_heads, PAGE, v_head_dim]).  `v_in_k`: the values
     are the leading `v_head_dim` columns of the key rows, so no value pages exist (a layer that caches one latent
-    row per position and reads it as key and as value)."""
+    row per position and reads it as key and as value).  `keep_first`: with a window, the first `keep_first`
+    positions of a sequence stay readable for as long as it lives (their pages are never handed back)."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     v_in_k: bool = False
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -162,6 +164,15 @@ class PendingSum:
     second: torch.Tensor
     scale_first: float = 1.0
     scale_second: float = 1.0
+
+
+@dataclass
+class ScaledDelta:
+    """A part's output that joins the residual stream times a constant:  x += scale * delta, formed in float32 by the
+    norm kernel that reads the stream next."""
+
+    delta: torch.Tensor
+    scale: float
 
 
 @dataclass

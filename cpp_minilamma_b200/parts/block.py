@@ -2,6 +2,8 @@
 
 `pre_norm` is the reference's layer (src/forward.cc:385-414):
     r = x + mixer(norm_in(x));   x' = r + feed_forward(norm_post(r))
+With `residual_mult` m (not in the reference) both outputs join the stream times m:  r = x + m mixer(..),
+x' = r + m feed_forward(..); a layer without a feed-forward ends at r.
 `parallel` (not in the reference) lets mixer and feed-forward read one norm:
     h = norm(x);   x' = x + mixer(h) + feed_forward(h)
 `sandwich` (not in the reference) puts a norm behind each sub-layer as well as in front of it:
@@ -16,7 +18,7 @@ from __future__ import annotations
 from typing import List
 
 from .mlp import NoFeedForward
-from .base import Block, NormedDelta, PendingSum, ResidualTarget, register_part
+from .base import Block, NormedDelta, PendingSum, ResidualTarget, ScaledDelta, register_part
 
 
 def _offer(x, norm, writer, reader):
@@ -27,17 +29,31 @@ def _offer(x, norm, writer, reader):
 
 
 class PreNormBlock(Block):
+    """params: residual_mult (default 1): the factor on both sub-layers' outputs where they join the stream."""
+
     capturable = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.mult = float(params.get("residual_mult", 1.0))
 
     def norm_names(self) -> List[str]:
         return ["input", "post_mixer"]
 
     def first_reader(self, layer):
-        return (layer.norms["input"], layer.mixer) if layer.mixer.takes_prenormed else None
+        # a factor on the outputs is applied by the norm kernel that adds them: no norm is folded away then
+        return (layer.norms["input"], layer.mixer) if layer.mixer.takes_prenormed and self.mult == 1.0 else None
 
     def forward(self, step, x, pending, layer, cache, next_reader=None):
         h = layer.norms["input"].forward(step, x, pending)
         post = layer.norms["post_mixer"]
+        if self.mult != 1.0 or isinstance(layer.feed_forward, NoFeedForward):
+            mixed = layer.mixer.forward(step, h, cache)
+            mixed = ScaledDelta(mixed, self.mult) if self.mult != 1.0 else mixed
+            if isinstance(layer.feed_forward, NoFeedForward):
+                return mixed
+            fed = layer.feed_forward.forward(step, post.forward(step, x, mixed))
+            return ScaledDelta(fed, self.mult) if self.mult != 1.0 else fed
         into = _offer(x, post, layer.mixer, layer.feed_forward)
         mixed = layer.mixer.forward(step, h, cache, into=into) if into else layer.mixer.forward(step, h, cache)
         h = post.forward(step, x, mixed)

@@ -11,7 +11,10 @@ Options beyond that, each a parameter: a query temperature (q at position p time
 every) + 1)); a sink in the softmax (weights exp(s_j) / (1 + sum_j exp(s_j)): one more key that scores 0 and carries
 no value), or a learned one (exp(c_h) in place of the 1, c_h a number per query head that no scale touches); values
 that are the keys themselves as projected, before norm and rotation (no W_v; dv == d); an output gate read from the mixer's own input, one number per head (head h's output times
-sigmoid(W_g h)_h) or one per element, applied before W_o.
+sigmoid(W_g h)_h) or one per element, applied before W_o; a smooth cap on the scores, s <- cap * tanh(s / cap) after the
+scale; a window that keeps the sequence's first tokens (key j < keep_first stays visible whatever its distance, at its own
+position); keys and values that are another layer's (`kv_shared`: the layer has queries and an output projection only and
+reads the cache of the schedule entry named by its own entry's `cache_of`, with its own mask, scale and cap).
 
 Chunks count from position 0 of the sequence, not from where a step's tokens begin.  Keys and values live in
 the paged cache; a chunked layer asks the cache to keep only what its chunk can still reach (a window of one
@@ -47,6 +50,12 @@ class ChunkedAttention(Mixer):
       out_name                                      workspace name of the result (default "o"; two mixers whose results
                                                     are both pending need two)
       gate                                          None, "head" or "element": an output gate sigmoid(W_g h), names["g"]
+      softcap                                       0 / None, or the cap c: score <- c * tanh(score / c) after the scale
+      keep_first                                    with a window: keys at positions below this stay visible
+      kv_shared                                     True: no names["k"] / ["v"]; keys and values are read from the cache
+                                                    of another schedule entry (the entry's `cache_of`)
+      cache_window, cache_keep_first                what the cache must keep when other layers read this layer's keys
+                                                    with masks of their own (default: this layer's window / keep_first)
       names                                         {"q","k","v","o"} (and "g"): tensor names
     """
 
@@ -75,6 +84,17 @@ class ChunkedAttention(Mixer):
         if self.v_from_k and self.dv != self.d:
             raise ValueError(f"attention: values that are the keys have their size, got {self.dv} / {self.d}")
         self.out_name = params.get("out_name") or "o"
+        self.softcap = float(params.get("softcap") or 0.0)
+        self.keep_first = int(params.get("keep_first") or 0) if self.window > 0 else 0
+        self.kv_shared = bool(params.get("kv_shared", False))
+        self.cache_window = int(params["cache_window"]) if params.get("cache_window") is not None else self.window
+        self.cache_keep_first = int(params["cache_keep_first"]) if params.get("cache_keep_first") is not None else self.keep_first
+        if self.softcap < 0 or self.keep_first < 0:
+            raise ValueError(f"attention: a cap of {self.softcap} or {self.keep_first} kept tokens")
+        if self.keep_first and self.chunk:
+            raise ValueError("attention: kept first tokens go with a window, not with chunks")
+        if self.kv_shared and (self.v_from_k or params.get("qk_norm")):
+            raise ValueError("attention: a layer that reads another layer's keys has no key options of its own")
         self.gate = params.get("gate") or None
         if self.gate not in (None, "head", "element"):
             raise ValueError(f"attention: gate {self.gate!r} is neither 'head' nor 'element'")
@@ -94,11 +114,12 @@ class ChunkedAttention(Mixer):
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.ctx.hidden_size
-        specs = [WeightSpec(self.names["q"], (self.n_heads * self.d, D)),
-                 WeightSpec(self.names["k"], (self.n_kv_heads * self.d, D)),
-                 WeightSpec(self.names["o"], (D, self.n_heads * self.dv))]
-        if not self.v_from_k:
-            specs.insert(2, WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)))
+        specs = [WeightSpec(self.names["q"], (self.n_heads * self.d, D))]
+        if not self.kv_shared:
+            specs.append(WeightSpec(self.names["k"], (self.n_kv_heads * self.d, D)))
+            if not self.v_from_k:
+                specs.append(WeightSpec(self.names["v"], (self.n_kv_heads * self.dv, D)))
+        specs.append(WeightSpec(self.names["o"], (D, self.n_heads * self.dv)))
         if self.sink_name:
             specs.append(WeightSpec(self.sink_name, (self.n_heads,), kind="vector", init="normal"))
         if self.gate:
@@ -113,7 +134,8 @@ class ChunkedAttention(Mixer):
 
     def bind(self, store) -> None:
         # the gate reads the same rows as q, k and v: its matrix rides behind theirs in the one fused product
-        parts = [p for p in ("q", "k", "v", "g") if (p != "v" or not self.v_from_k) and (p != "g" or self.gate)]
+        parts = [p for p in ("q", "k", "v", "g") if (p != "v" or not self.v_from_k) and (p != "g" or self.gate)
+                 and (p == "q" or p == "g" or not self.kv_shared)]
         mats = [store.take(self.names[p]) for p in parts]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
@@ -135,8 +157,10 @@ class ChunkedAttention(Mixer):
 
     def cache_need(self) -> CacheNeed:
         # a query reads nothing before its chunk's first key, which lies less than `chunk` positions back
-        reach = self.chunk if self.window <= 0 else (min(self.chunk, self.window) if self.chunk else self.window)
-        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.d, reach, self.dv if self.dv != self.d else 0))
+        window = self.cache_window
+        reach = self.chunk if window <= 0 else (min(self.chunk, window) if self.chunk else window)
+        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.d, reach, self.dv if self.dv != self.d else 0,
+                                   keep_first=self.cache_keep_first if reach > 0 and not self.chunk else 0))
 
     def _tensor_cores(self) -> bool:
         return K.local_attention_mma_supported(self.ctx.act_dtype, self.d, self.dv)
@@ -169,6 +193,8 @@ class ChunkedAttention(Mixer):
         act = self.ctx.act_dtype
         if cache.k is None:
             raise RuntimeError("attention: the cache view has no key/value storage")
+        if self.kv_shared and cache.owns_kv:
+            raise RuntimeError("attention: a layer without keys of its own must read another schedule entry's cache")
         qkv = self.qkv.forward(step, h, "qkv")
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         q = step.ws.buffer("q", (T, self.n_heads * self.d), act)
@@ -177,18 +203,21 @@ class ChunkedAttention(Mixer):
                                   self.n_kv_heads, self.d, self.dv, self.rot,
                                   bool(self.position.interleaved) if self.position is not None else False,
                                   float(self.qk_norm["eps"]) if self.qk_norm else 0.0, q_temp=self.q_temp,
-                                  v_from_k=self.v_from_k)
+                                  v_from_k=self.v_from_k, write_kv=not self.kv_shared)
         out = step.ws.buffer("attn", (T, self.n_heads * self.dv), act)
         self._attend(step, q, cache, out)
         if self.gate:
-            gate_col = self.n_heads * self.d + self.n_kv_heads * (self.d if self.v_from_k else self.d + self.dv)
+            gate_col = self.n_heads * self.d + (0 if self.kv_shared else
+                                                self.n_kv_heads * (self.d if self.v_from_k else self.d + self.dv))
             K.heads_gate(out, qkv, gate_col, out, self.n_heads, self.dv, per_head=self.gate == "head")
         return self.o.forward(step, out, self.out_name)
 
     def _attend(self, step, q, cache, out) -> None:
         act = self.ctx.act_dtype
         learned = self.sink_values  # a sink with a score of its own per head, or None
-        if (step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+        extra = {"keep_first": self.keep_first, "softcap": self.softcap}
+        plain = not self.keep_first and not self.softcap  # what the Llama attention's kernels know
+        if (plain and step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
                 and not (self.chunk and self.window) and act == torch.bfloat16
                 and (not self.sink or K.USE_TENSOR_CORE_DECODE)):
             # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
@@ -207,10 +236,10 @@ class ChunkedAttention(Mixer):
             K.local_attention_heads(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     cache.block_table, out, step.n_seqs, self.n_heads, self.n_kv_heads, self.d, self.dv,
                                     self.chunk, self.window, self.scale, sink=self.sink, n_splits=splits, scratch=scratch,
-                                    sink_values=learned)
+                                    sink_values=learned, **extra)
             return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+        if plain and tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
             # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
             # which knows the chunk mask too
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
@@ -223,11 +252,11 @@ class ChunkedAttention(Mixer):
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                     tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out, self.n_heads,
                                     self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
-                                    sink=self.sink, sink_values=learned)
+                                    sink=self.sink, sink_values=learned, **extra)
             return
         K.local_attention(q, cache.k, cache.v, step.tok_pos, step.tok_seq, step.seq_slot, cache.block_table, out,
                           self.n_heads, self.n_kv_heads, self.d, self.dv, self.chunk, self.window, self.scale,
-                          sink=self.sink, sink_values=learned)
+                          sink=self.sink, sink_values=learned, **extra)
 
 
 register_part("mixer", "chunked_attention", ChunkedAttention)

@@ -17,8 +17,8 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """params: vocab, name; optional `norm`: PartSpec of a norm applied to the looked-up rows (on the
-    float32 stream itself) before the first layer."""
+    """params: vocab, name; optional `scale`: a factor on the looked-up rows (applied in float32); optional `norm`:
+    PartSpec of a norm applied to the looked-up rows (on the float32 stream itself) before the first layer."""
 
     capturable = True
 
@@ -29,6 +29,7 @@ class TokenEmbedding(Part):
         self.vocab = int(params["vocab"])
         self.name = params["name"]
         self.table: Optional[torch.Tensor] = None
+        self.row_scale = float(params.get("scale", 1.0))
         self.norm = build_part("norm", params["norm"], ctx) if params.get("norm") else None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -46,7 +47,7 @@ class TokenEmbedding(Part):
 
     def forward(self, step, tokens: torch.Tensor) -> torch.Tensor:
         x = step.ws.buffer("x", (tokens.shape[0], self.ctx.hidden_size), torch.float32)
-        K.embedding(tokens, self.table, x)
+        K.embedding(tokens, self.table, x, self.row_scale)
         if self.norm is not None:
             self.norm.forward_in_place(x)
         return x
@@ -101,7 +102,8 @@ class PairHashEmbedding(TokenEmbedding):
 
 
 class LMHead(Part):
-    """params: vocab, name, tied_to (name of the embedding tensor, or None)."""
+    """params: vocab, name, tied_to (name of the embedding tensor, or None), scale (a factor on the float32 logits,
+    default 1)."""
 
     capturable = True
 
@@ -112,6 +114,7 @@ class LMHead(Part):
         self.vocab = int(params["vocab"])
         self.name = params["name"]
         self.tied_to = params.get("tied_to")
+        self.scale = float(params.get("scale", 1.0))
         self.linear: Optional[Linear] = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -127,7 +130,10 @@ class LMHead(Part):
         return self.linear.parameter_bytes()
 
     def forward(self, step, h: torch.Tensor, out_name: str = "logits") -> torch.Tensor:
-        return self.linear.forward(step, h, out_name, out_dtype=torch.float32)
+        logits = self.linear.forward(step, h, out_name, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            K.scale_(logits, self.scale)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

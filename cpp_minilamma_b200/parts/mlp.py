@@ -5,7 +5,9 @@ The reference's FfnForward (src/forward.cc:313-322) with SiLU as x / (1 + exp(-x
 [2I, D] matrix so that one product feeds the activation kernel; when I is a multiple of
 8 their rows are interleaved in blocks of 8 (gate rows 0-7, up rows 0-7, gate rows
 8-15, ...), which puts a gate value and its up value into the same thread of a
-tensor-core accumulator tile.
+tensor-core accumulator tile.  With biases (not in the reference) the form is
+down( silu(gate(h) + b_g) * (up(h) + b_u) ) + b_d: the gate and up biases are added in float32 inside the activation
+kernel, in the fused matrix's row order.
 """
 from __future__ import annotations
 
@@ -34,7 +36,8 @@ def fuse_gate_up(gate: torch.Tensor, up: torch.Tensor):
 
 class SwiGLUFeedForward(FeedForward):
     """params: intermediate, names {"gate","up","down"} (tensor name stems, ".weight" is appended; with
-    `bare_names` they are the tensor names themselves)."""
+    `bare_names` they are the tensor names themselves); bias_names {"gate","up","down"}: tensor names of the three
+    biases, or None for a feed-forward without biases; out_name: workspace name of the result (default "down")."""
 
     capturable = True
     takes_prenormed = True  # the gate/up product may read rows whose norm it finishes itself
@@ -45,17 +48,33 @@ class SwiGLUFeedForward(FeedForward):
         self.inter = int(params["intermediate"])
         suffix = "" if params.get("bare_names") else ".weight"
         self.names = {k: v + suffix for k, v in dict(params["names"]).items()}
+        self.bias_names = dict(params["bias_names"]) if params.get("bias_names") else None
+        self.out_name = params.get("out_name") or "down"
+        if self.bias_names:  # the products that fold norms away know no bias: this instance takes plain rows
+            self.takes_prenormed = self.adds_residual = False
+        self.gate_up_bias = self.down_bias = None
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
         self.block = 0
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.ctx.hidden_size
-        return [WeightSpec(self.names["gate"], (self.inter, D)),
-                WeightSpec(self.names["up"], (self.inter, D)),
-                WeightSpec(self.names["down"], (D, self.inter))]
+        specs = [WeightSpec(self.names["gate"], (self.inter, D)),
+                 WeightSpec(self.names["up"], (self.inter, D)),
+                 WeightSpec(self.names["down"], (D, self.inter))]
+        if self.bias_names:
+            specs += [WeightSpec(self.bias_names["gate"], (self.inter,), kind="vector"),
+                      WeightSpec(self.bias_names["up"], (self.inter,), kind="vector"),
+                      WeightSpec(self.bias_names["down"], (D,), kind="vector")]
+        return specs
 
     def bind(self, store) -> None:
+        if self.bias_names:
+            # the two biases in the fused matrix's row order (as columns [inter, 1] they interleave like its rows)
+            fused_bias, _ = fuse_gate_up(store.take(self.bias_names["gate"]).float().view(-1, 1),
+                                         store.take(self.bias_names["up"]).float().view(-1, 1))
+            self.gate_up_bias = fused_bias.view(-1).contiguous()
+            self.down_bias = store.take(self.bias_names["down"]).float().contiguous()
         fused, self.block = fuse_gate_up(store.take(self.names["gate"]), store.take(self.names["up"]))
         self.gate_up = Linear(fused, self.names["gate"] + "+up")
         self.down = Linear(store.take(self.names["down"]), self.names["down"])
@@ -64,6 +83,13 @@ class SwiGLUFeedForward(FeedForward):
         return self.gate_up.parameter_bytes() + self.down.parameter_bytes()
 
     def forward(self, step, h, into=None):
+        if self.gate_up_bias is not None:
+            gu = self.gate_up.forward(step, h, "gu")
+            act = step.ws.buffer("act", (h.shape[0], self.inter), gu.dtype)
+            K.swiglu(gu, act, self.block, bias=self.gate_up_bias)
+            out = self.down.forward(step, act, self.out_name)
+            K.add_bias(out, self.down_bias)
+            return out
         values, row_norm = (h.values, K.RowNorm(h.sumsq, h.partials, h.eps)) if isinstance(h, PreNormed) else (h, None)
         rows = values.shape[0]
         w = self.gate_up.weight
@@ -85,7 +111,7 @@ class SwiGLUFeedForward(FeedForward):
             gu = self.gate_up.forward(step, h, "gu")
             act = step.ws.buffer("act", (rows, self.inter), gu.dtype)
             K.swiglu(gu, act, self.block)
-        return self.down.forward(step, act, "down", into=into)
+        return self.down.forward(step, act, self.out_name, into=into)
 
 
 class GeluFeedForward(FeedForward):

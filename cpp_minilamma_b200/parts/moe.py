@@ -8,7 +8,9 @@
 Other forms, each a parameter: scores over all experts (s = softmax(z) over every expert; the choice goes by s + a
 stored correction, the weights are the chosen s over their sum, times a constant); experts without a gate,
 W_down gelu(W_up h); identity experts - the router's last rows belong to experts without tensors, whose output is
-their input times the weight; a gate on the shared expert, sigmoid(w_g . h), one number per token, whose row rides
+their input times the weight; sigmoid scores with a choice limited to groups (s = sigmoid(z); the experts form equal
+groups of neighbours, a group scores the sum of its two largest s, only experts of the best `keep` groups can be chosen;
+the weights are the chosen s over their sum); a gate on the shared expert, sigmoid(w_g . h), one number per token, whose row rides
 behind the router's so that the routing kernel forms it.
 
 The experts' matrices are stacked ([E, 2 I, D] gate rows then up rows, and [E, D, I]); the routing stays on the
@@ -37,8 +39,9 @@ class RoutedFeedForward(FeedForward):
       shared                          None, or the params of a feed-forward part that every token also goes through
       shared_kind                     that part's kind ("swiglu" by default)
       shared_gate                     None, or the tensor name of a [1, D] matrix: the shared output times sigmoid(w . h)
-      scoring                         "chosen" (softmax over the chosen logits, the default) or "all" (see above;
-                                      names["correction"] is then the correction, `scale` the constant)
+      scoring                         "chosen" (softmax over the chosen logits, the default), "all" (see above;
+                                      names["correction"] is then the correction, `scale` the constant) or
+                                      "sigmoid_groups" (`groups` = {"count", "keep"}; `scale` the constant)
       identity                        experts behind the `experts` real ones that hand their input on (router rows
                                       experts .. experts + identity - 1)
       expert_form                     "swiglu" (default) or "gelu" (names' p is then one of up, down)
@@ -56,9 +59,18 @@ class RoutedFeedForward(FeedForward):
         self.has_bias = bool(params.get("router_bias", False))
         self.identity = int(params.get("identity") or 0)
         self.routed = self.experts + self.identity  # rows of the router
-        self.all_scores = (params.get("scoring") or "chosen") == "all"
-        if params.get("scoring") not in (None, "chosen", "all"):
-            raise ValueError(f"routed feed-forward: scoring {params.get('scoring')!r} is neither 'chosen' nor 'all'")
+        self.all_scores = (params.get("scoring") or "chosen") in ("all", "sigmoid_groups")
+        if params.get("scoring") not in (None, "chosen", "all", "sigmoid_groups"):
+            raise ValueError(f"routed feed-forward: scoring {params.get('scoring')!r} is none of 'chosen', 'all', 'sigmoid_groups'")
+        self.groups = None
+        if params.get("scoring") == "sigmoid_groups":
+            groups = params.get("groups") or {"count": 1, "keep": 1}
+            self.groups = (int(groups["count"]), int(groups["keep"]))
+            count, keep = self.groups
+            if count < 1 or self.experts % count or not 1 <= keep <= count or int(params.get("identity") or 0):
+                raise ValueError(f"routed feed-forward: {self.experts} experts in {count} groups of which {keep} are kept")
+            if int(params["top"]) > keep * (self.experts // count):
+                raise ValueError(f"routed feed-forward: top {params['top']} exceeds the experts of {keep} groups")
         self.scale = float(params.get("scale", 1.0))
         self.gelu = (params.get("expert_form") or "swiglu") == "gelu"
         if params.get("expert_form") not in (None, "swiglu", "gelu"):
@@ -152,7 +164,7 @@ class RoutedFeedForward(FeedForward):
             torch.mm(wide, self.router.t(), out=logits)
         shared_gate = ws.buffer("moe.shared_gate", (T,), torch.float32) if self.shared_gate_name else None
         K.moe_route(h, self.router, self.router_bias, chosen, weight, self.top, logits=logits, all_scores=self.all_scores,
-                    scale=self.scale, gate_out=shared_gate)
+                    scale=self.scale, gate_out=shared_gate, groups=self.groups)
         # bfloat16: tiles of 64 rows on tensor cores at every size - with few rows per expert the products stream each
         # touched expert's weights once, and a mostly empty tile costs nothing that memory does not hide
         mma = K.USE_TENSOR_CORE_MOE and K.moe_mma_supported(act, D, self.inter)

@@ -20,7 +20,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import kernels as K
-from .base import BuildContext, Norm, NormedDelta, PendingSum, PreNormed, WeightSpec, register_part
+from .base import BuildContext, Norm, NormedDelta, PendingSum, PreNormed, ScaledDelta, WeightSpec, register_part
 
 
 def _delta_parts(delta):
@@ -32,7 +32,9 @@ def _delta_parts(delta):
             raise RuntimeError("a delta can only pass a norm of the RMS form on its way into the stream")
         delta = delta.delta
     first, second, s1, s2 = delta, None, 1.0, 1.0
-    if isinstance(delta, PendingSum):
+    if isinstance(delta, ScaledDelta):
+        first, s1 = delta.delta, delta.scale
+    elif isinstance(delta, PendingSum):
         first, second, s1, s2 = delta.first, delta.second, delta.scale_first, delta.scale_second
     if norm is None and s1 == 1.0 and s2 == 1.0:
         return first, second, None
@@ -120,7 +122,7 @@ class LayerNorm(Norm):
             raise RuntimeError(f"{self.name}: a layer norm cannot finish rows that were prepared for another norm")
         n = x.shape[0] if rows is None else rows.shape[0]
         out = step.ws.buffer(out_name, (n, self.width), self.ctx.act_dtype)
-        if isinstance(delta, NormedDelta) or (isinstance(delta, PendingSum) and (delta.scale_first != 1.0 or delta.scale_second != 1.0)):
+        if isinstance(delta, (NormedDelta, ScaledDelta)) or (isinstance(delta, PendingSum) and (delta.scale_first != 1.0 or delta.scale_second != 1.0)):
             raise RuntimeError(f"{self.name}: a layer norm adds its delta as it is (no norm or factor on the way in)")
         if isinstance(delta, PendingSum):
             # two parts that read one norm: add the first to the stream here, the second with the norm

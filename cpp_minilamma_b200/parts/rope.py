@@ -17,6 +17,8 @@ pair(t) = d ln(L0 / (2 pi t)) / (2 ln theta) - the pair whose wavelength makes t
 lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), d - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):
 f'_i = ramp_i f_i / factor + (1 - ramp_i) f_i, and cos and sin are both multiplied by 0.1 ln(factor) + 1.
 
+`scaling` of type "linear" (not in the reference) divides every frequency by `factor`.
+
 `interleaved` selects the pairing: True pairs (2i, 2i+1) (the reference's Normal type),
 False pairs (i, i + d/2) (its NeoX type), src/ops.cc:206-210.
 """
@@ -36,6 +38,8 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Dict[str,
     freqs = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / head_dim)
     if not scaling:
         return freqs
+    if scaling.get("type") == "linear":
+        return freqs / float(scaling["factor"])
     if scaling.get("type") == "yarn":
         factor, original = float(scaling["factor"]), float(scaling["original"])
 

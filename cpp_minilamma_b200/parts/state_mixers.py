@@ -15,6 +15,12 @@ write, and both normalise every head's o by its root mean square before a gate a
 `gated_linear_attention`  a decay per head and key channel, g = sigmoid(W_a2 W_a1 h + b)^(1 / tau), u = v, q / sqrt(d);
                      out = W_o (o / rms(o) * w * silu(W_g h))
 
+`state_space`        (the state-space duality form) one projection W_in h = [z | x | B | C | dt]; x, B and C pass a short
+                     causal convolution with a bias and silu; dt = softplus(dt + bias) per head; one decay per token
+                     and head, g = exp(-exp(A_h) dt); k = B and q = C are shared by the heads of a group, u = dt x;
+                     o + D_h x, times silu(z), normalised in a few equal parts of the row, times a weight, then W_o;
+                     the last taps - 1 convolution inputs of a sequence are state too
+
 What enters the recurrence is float32 (decays, step sizes, gates, unit vectors, the state); the projections are
 products in the run's dtype.  Sizes, decays, tap counts and eps are parameters.
 """
@@ -275,6 +281,87 @@ class GatedLinearAttention(Mixer):
         return self.o.forward(step, gated, self.out_name)
 
 
+class StateSpace(Mixer):
+    """params: n_heads, n_groups (heads of one group share B and C), v_head_dim (columns of x per head), state (rows of
+    the state per head: the size of B and C), conv (taps), norm_groups (equal parts of the row that are normalised
+    each by itself), eps (of that norm), out_name (workspace name of the result, default "o"),
+    names: tensor names for "in", "conv", "conv_bias", "dt_bias", "A_log", "D", "norm", "o"."""
+
+    capturable = True
+
+    def __init__(self, params, ctx: BuildContext):
+        super().__init__(params, ctx)
+        self.n_heads = int(params["n_heads"])
+        self.n_groups = int(params["n_groups"])
+        self.dv = int(params["v_head_dim"])
+        self.d = int(params["state"])
+        self.taps = int(params["conv"])
+        self.parts = int(params.get("norm_groups") or 1)
+        self.eps = float(params["eps"])
+        self.names = dict(params["names"])
+        self.out_name = params.get("out_name") or "o"
+        if self.n_groups < 1 or self.n_heads % self.n_groups:
+            raise ValueError(f"state space: {self.n_heads} heads are not a multiple of {self.n_groups} groups")
+        if self.taps < 1:
+            raise ValueError("state space: the convolution needs at least one tap")
+        self.inner = self.n_heads * self.dv
+        if self.parts < 1 or self.inner % self.parts:
+            raise ValueError(f"state space: {self.inner} columns cannot be normalised in {self.parts} equal parts")
+        self.channels = self.inner + 2 * self.n_groups * self.d        # what passes the convolution: x, B, C
+        self.rows = 2 * self.inner + 2 * self.n_groups * self.d + self.n_heads
+        self.proj: Optional[Linear] = None
+        self.o: Optional[Linear] = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D, H, n = self.ctx.hidden_size, self.n_heads, self.names
+        return [WeightSpec(n["in"], (self.rows, D)),
+                WeightSpec(n["conv"], (self.channels, self.taps), kind="vector"),
+                WeightSpec(n["conv_bias"], (self.channels,), kind="vector"),
+                WeightSpec(n["dt_bias"], (H,), kind="vector"), WeightSpec(n["A_log"], (H,), kind="vector"),
+                WeightSpec(n["D"], (H,), kind="vector", init="norm"),
+                WeightSpec(n["norm"], (self.inner,), kind="vector", init="norm"),
+                WeightSpec(n["o"], (D, self.inner))]
+
+    def bind(self, store) -> None:
+        n = self.names
+        self.proj = Linear(_pad_rows(store.take(n["in"])), n["in"])
+        self.conv_w = store.take(n["conv"]).contiguous()
+        self.conv_b = store.take(n["conv_bias"])
+        self.dt_bias = store.take(n["dt_bias"])
+        self.a_log = store.take(n["A_log"])
+        self.skip = store.take(n["D"])
+        self.norm_w = store.take(n["norm"])
+        self.o = Linear(store.take(n["o"]), n["o"])
+
+    def parameter_bytes(self) -> int:
+        return self.proj.parameter_bytes() + self.o.parameter_bytes()
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(state=StateNeed((("S", (self.n_heads, self.d, self.dv)),
+                                          ("conv", (self.taps - 1, self.channels)))))
+
+    def forward(self, step, h, cache):
+        T, H, G, d, dv = h.shape[0], self.n_heads, self.n_groups, self.d, self.dv
+        ws = step.ws
+        proj = self.proj.forward(step, h, "ssd.proj")
+        q = ws.buffer("ssd.q", (T, G * d), torch.float32)
+        k = ws.buffer("ssd.k", (T, G * d), torch.float32)
+        u = ws.buffer("ssd.u", (T, self.inner), torch.float32)
+        xs = ws.buffer("ssd.x", (T, self.inner), torch.float32)
+        decay = ws.buffer("ssd.decay", (T, H), torch.float32)
+        K.ssd_prepare(proj, self.conv_w, self.conv_b, cache.state["conv"], self.a_log, self.dt_bias, step.tok_seq,
+                      step.seq_slot, step.seq_qstart, q, k, u, xs, decay, H, G, d, dv, self.taps)
+        K.conv_state_update(proj, cache.state["conv"], step.seq_slot, step.seq_qstart, step.seq_qlen, step.n_seqs,
+                            self.channels, self.taps, first_column=self.inner)
+        o = ws.buffer("ssd.o", (T, self.inner), torch.float32)
+        K.state_scan(q, k, u, None, None, None, cache.state["S"], o, step.seq_slot, step.seq_qstart, step.seq_qlen,
+                     step.n_seqs, H, G, d, dv, token_decay=decay)
+        gated = ws.buffer("ssd.gated", (T, self.inner), self.ctx.act_dtype)
+        K.gated_group_norm(o, xs, self.skip, proj, self.norm_w, gated, dv, self.parts, self.eps)
+        return self.o.forward(step, gated, self.out_name)
+
+
+register_part("mixer", "state_space", StateSpace)
 register_part("mixer", "gated_linear_attention", GatedLinearAttention)
 register_part("mixer", "retention", Retention)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

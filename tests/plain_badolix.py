@@ -226,27 +226,37 @@ def dense_ff(h, w, prefix):
 
 
 def route(scores, top, count, keep):
-    """(chosen experts, weights) of one token's scores; ties go to the lower index."""
+    """(chosen experts, weights, margin) of one token's scores; ties go to the lower index.  The margin is the
+    smallest gap between something taken and the best thing left out (groups, then experts)."""
     E = scores.shape[0]
     per = E // count
     group_score = np.array([np.sort(scores[g * per:(g + 1) * per])[::-1][:2].sum() for g in range(count)])
-    kept = np.argsort(-group_score, kind="stable")[:keep]
+    order = np.argsort(-group_score, kind="stable")
+    kept = order[:keep]
+    margin = group_score[order[keep - 1]] - group_score[order[keep]] if keep < count else np.inf
     allowed = np.zeros(E, dtype=bool)
     for g in kept:
         allowed[g * per:(g + 1) * per] = True
     masked = np.where(allowed, scores, -np.inf)
-    chosen = np.argsort(-masked, kind="stable")[:top]
+    ranked = np.argsort(-masked, kind="stable")
+    chosen = ranked[:top]
+    if top < E and np.isfinite(masked[ranked[top]]):
+        margin = min(margin, masked[ranked[top - 1]] - masked[ranked[top]])
     s = scores[chosen]
-    return chosen, s / (s.sum() + 1e-20)
+    return chosen, s / (s.sum() + 1e-20), margin
 
 
-def routed_ff(h, w, prefix, mlp):
+def routed_ff(h, w, prefix, mlp, margins=None):
+    """`margins`: a list that receives one array per call, the routing margin of every token."""
     router = mlp["router"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     scores = sigmoid(h @ w[prefix + "router"].T)
     out = np.zeros_like(h)
+    token_margin = np.zeros(h.shape[0])
+    if margins is not None:
+        margins.append(token_margin)
     for t in range(h.shape[0]):
-        chosen, weights = route(scores[t], int(router["top"]), int(groups["count"]), int(groups["keep"]))
+        chosen, weights, token_margin[t] = route(scores[t], int(router["top"]), int(groups["count"]), int(groups["keep"]))
         for e, weight in zip(chosen, weights):
             p = f"{prefix}e{e}."
             out[t] += weight * ((silu(h[t] @ w[p + "gate"].T) * (h[t] @ w[p + "up"].T)) @ w[p + "down"].T)
@@ -256,8 +266,9 @@ def routed_ff(h, w, prefix, mlp):
 # --------------------------------------------------------------------------- #
 # the whole model                                                              #
 # --------------------------------------------------------------------------- #
-def forward(config, w, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence from its first token (and the stream after every layer)."""
+def forward(config, w, tokens, return_layers=False, margins=None):
+    """Logits [T, vocab] of one sequence from its first token (and the stream after every layer).  `margins`: a list
+    that receives every routed layer's margins per token."""
     eps = float(config["norm"]["eps"])
     mult = float(config.get("residual_mult", 1.0))
     tokens = np.asarray(tokens, dtype=np.int64)
@@ -283,7 +294,8 @@ def forward(config, w, tokens, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             h = rms(x, eps) * w[prefix + "norm2"]
-            x = x + mult * (dense_ff(h, w, prefix + "mlp.") if mlp["kind"] == "dense" else routed_ff(h, w, prefix + "mlp.", mlp))
+            x = x + mult * (dense_ff(h, w, prefix + "mlp.") if mlp["kind"] == "dense"
+                            else routed_ff(h, w, prefix + "mlp.", mlp, margins))
         streams.append(x.copy())
     logits = (rms(x, eps) * w["final.norm"]) @ w["embed"].T * float(config.get("logit_scale", 1.0))
     return (logits, np.stack(streams)) if return_layers else logits

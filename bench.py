@@ -539,6 +539,72 @@ def sopanex_rooflines(size, tokens, batch, context, peaks):
     return out
 
 
+def badolix_config(size):
+    """Six layers: window attention (1,024 positions and the first 64 tokens, capped scores, 128 dimensions rotated at
+    divided frequencies), window attention that reads the first layer's keys and values, latent attention (the Malulorn
+    decoder's sizes, frequencies under a ramp), a state-space mixer (inner size 2 x width in heads of 64, states of 128,
+    8 groups, 4 taps), window attention, latent attention; dense feed-forwards with biases and routed ones (4 of 16
+    experts of ff / 4, chosen inside 2 of 4 groups: the dense layer's work per token) take turns."""
+    import cpp_minilamma_b200 as ml
+    s = DESIGN_SIZES[size]
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": s["ff"] // 4}}
+    window = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+              "mask": {"size": 1024, "keep_first": 64}, "rot": {"base": 500000.0, "dims": 128, "scaling": {"factor": 8.0}}}
+    latent = {"heads": s["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 192 ** -0.5,
+              "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 1.0}}}
+    ssm = {"heads": 2 * s["width"] // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+    layers = [{"type": "attention", "mixer": window, "mlp": dense},
+              {"type": "attention", "mixer": dict(window, kv_from=0), "mlp": moe},
+              {"type": "latent_attention", "mixer": latent, "mlp": dense},
+              {"type": "mamba2", "mixer": ssm, "mlp": moe},
+              {"type": "attention", "mixer": window, "mlp": dense},
+              {"type": "latent_attention", "mixer": latent, "mlp": moe}]
+    return ml.config_from_dict({"architecture": "Badolix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+                                "embedding": {"scale": 2.0}, "residual_mult": 0.7, "logit_scale": 0.5, "layers": layers,
+                                "torch_dtype": "bfloat16"})
+
+
+def badolix_rooflines(size, tokens, batch, context, peaks):
+    """As `design_rooflines`, for the kernels of the Badolix decoder and their like in the Malulorn decoder."""
+    s = DESIGN_SIZES[size]
+    H, G, d, D, ff = s["heads"], s["kv_heads"], 128, s["width"], s["ff"]
+    rank, row = 192, 256
+    E, top, eff = 16, 4, ff // 4
+    Hs, P, N, Gs, taps = 2 * D // 64, 64, 128, 8, 4
+    inner = Hs * P
+    out = {k: v for k, v in malulorn_rooflines(size, tokens, batch, context, peaks).items() if k[0] == "malulorn"}
+    causal = tokens * (tokens + 1) // 2
+    seen = sum(min(i + 1, 1024 + 64) for i in range(tokens))            # keys a prompt token sees: its window and the kept tokens
+    out["badolix", "prefill", "local_attention_mma (window)"] = ("tensor", 2.0 * H * seen * 2 * d)
+    out["badolix", "prefill", "local_attention_mma"] = ("tensor", 2.0 * H * causal * (row + rank))
+    qkv = (H * d + 2 * G * d) * 2
+    for kind, n, seqs in (("prefill", tokens, 1), ("decode", batch, batch)):
+        out["badolix", kind, "local_attention_prepare"] = ("hbm", n * (2 * qkv + 2 * H * d * 2) / 3)  # two layers of three write keys
+        out["badolix", kind, "latent_prepare"] = ("hbm", n * (H * 64 * 4 + row * 4 + rank * 2))
+        out["badolix", kind, "moe_route"] = ("hbm", n * D * 2 + E * D * 4)
+        out["badolix", kind, "moe_combine"] = ("hbm", n * D * (top * 4 + 2))
+        out["badolix", kind, "rmsnorm"] = ("hbm", n * D * (4 + 4 + 2 + 2))
+        out["badolix", kind, "swiglu"] = ("hbm", n * ff * (4 + 2))
+        out["badolix", kind, "add_bias"] = ("hbm", n * D * 4)
+        # the state-space mixer: what a step must move at least - the projection's row, the float32 inputs and outputs
+        # of the recurrence per token, and in a decode step the state once in and once out
+        gn = Gs * N
+        out["badolix", kind, "ssd_prepare"] = ("hbm", n * ((inner + 2 * gn + Hs) * 2 + (2 * inner + 2 * gn + Hs) * 4))
+        out["badolix", kind, "state_scan (token decay)"] = ("hbm", n * (2 * inner + 2 * gn + Hs) * 4 + seqs * Hs * N * P * 8)
+        out["badolix", kind, "gated_group_norm"] = ("hbm", n * inner * (4 + 4 + 2 + 2))
+        out["badolix", kind, "conv_state_update"] = ("hbm", seqs * (taps - 1) * (inner + 2 * gn) * (2 + 4))
+    visible = min(context, 1024 + 64)
+    out["badolix", "decode", "local_attention_heads (window)"] = ("hbm", batch * visible * G * 2 * d * 2)
+    out["badolix", "decode", "local_attention_heads"] = ("hbm", batch * context * row * 2)
+    out["badolix", "prefill", "moe_gate_up_mma"] = ("tensor", 2.0 * tokens * top * 2 * eff * D)
+    out["badolix", "prefill", "moe_down_mma"] = ("tensor", 2.0 * tokens * top * eff * D)
+    touched = min(E, batch * top)
+    out["badolix", "decode", "moe_gate_up_mma"] = ("hbm", touched * 2 * eff * D * 2)
+    out["badolix", "decode", "moe_down_mma"] = ("hbm", touched * eff * D * 2)
+    return out
+
+
 def llama_like_config(size):
     import cpp_minilamma_b200 as ml
     s = DESIGN_SIZES[size]
@@ -617,9 +683,11 @@ def bench_design(args):
     warmup, steps = max(args.warmup, 3), max(min(args.steps, 64), 8)
     tokens, batch, context = PREFILL_TOKENS, 64, 1024
     design = args.design
-    make_config = {"kupirax": kupirax_config, "malulorn": malulorn_config, "sopanex": sopanex_config}[design]
-    rooflines = {"kupirax": design_rooflines, "malulorn": malulorn_rooflines, "sopanex": sopanex_rooflines}[design]
-    beside, beside_config = ("malulorn", malulorn_config) if design == "sopanex" else ("llama", llama_like_config)
+    make_config = {"kupirax": kupirax_config, "malulorn": malulorn_config, "sopanex": sopanex_config,
+                   "badolix": badolix_config}[design]
+    rooflines = {"kupirax": design_rooflines, "malulorn": malulorn_rooflines, "sopanex": sopanex_rooflines,
+                 "badolix": badolix_rooflines}[design]
+    beside, beside_config = ("malulorn", malulorn_config) if design in ("sopanex", "badolix") else ("llama", llama_like_config)
     result = {"design": design, "beside": beside, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
               "prefill_tokens": tokens, "decode_prompts": "uniform[128,1024)", "steps": steps, "warmup": warmup,
               "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "source": peaks["source"]},
@@ -688,9 +756,9 @@ def main():
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31_8b", help="model shape of the --profile step")
     parser.add_argument("--batch", type=int, default=BATCH, help="batch of the --profile decode step")
     parser.add_argument("--context", type=int, default=1024, help="prompt length of the --profile decode step")
-    parser.add_argument("--design", choices=["kupirax", "malulorn", "sopanex"], default=None,
+    parser.add_argument("--design", choices=["kupirax", "malulorn", "sopanex", "badolix"], default=None,
                         help="instead of the default workload: prompt and decode throughput and kernel times of that "
-                             "decoder beside the Llama decoder (sopanex: beside the Malulorn decoder) at equal sizes")
+                             "decoder beside the Llama decoder (sopanex, badolix: beside the Malulorn decoder) at equal sizes")
     parser.add_argument("--size", choices=sorted(DESIGN_SIZES), default=None, help="one size of --design (default: all)")
     args = parser.parse_args()
 

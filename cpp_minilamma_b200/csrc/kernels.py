@@ -1130,7 +1130,7 @@ def local_attention_tiles(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
         _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(0), ctypes.c_int(1), _ptr(None),
         ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
-        "local_attention_mma")
+        "local_attention_mma (window)" if keep_first or softcap else "local_attention_mma")
 
 
 def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, block_table, out, n_seqs: int,
@@ -1159,7 +1159,7 @@ def local_attention_heads(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, se
         ctypes.c_int(window), ctypes.c_int(block_table.shape[1]), ctypes.c_float(scale), ctypes.c_int(int(sink)),
         _ptr(sink_values), ctypes.c_int(int(v_in_k)), ctypes.c_int(1), ctypes.c_int(n_splits),
         _ptr(scratch if n_splits > 1 else None), ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
-        "local_attention_heads", kernels=2 if n_splits > 1 else 1)
+        "local_attention_heads (window)" if keep_first or softcap else "local_attention_heads", kernels=2 if n_splits > 1 else 1)
 
 
 def local_attention_heads_scratch(n_seqs: int, n_heads: int, dv: int, n_splits: int) -> int:

@@ -731,7 +731,10 @@ def bench_design(args):
             for (m, kind, name), (bound, amount) in expected.items():
                 if m != model:
                     continue
-                for key in [k for k in table if k == f"{kind}: {name}" or k.startswith(f"{kind}: {name} (")]:
+                # a kernel's launches may carry a suffix in brackets; a suffix with an entry of its own keeps that entry
+                own = {f"{k2}: {n2}" for (m2, k2, n2) in expected if m2 == model}
+                for key in [k for k in table if k == f"{kind}: {name}"
+                            or (k.startswith(f"{kind}: {name} (") and k not in own)]:
                     us = table[key]["us_per_call"]
                     peak = peaks["hbm_gbs"] * 1e9 if bound == "hbm" else peaks["bf16_tflops"] * 1e12
                     table[key].update(bound=bound, frac=round(amount / (us * 1e-6) / peak, 4))

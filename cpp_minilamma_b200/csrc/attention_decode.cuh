@@ -42,6 +42,10 @@ struct DecodeMmaArgs {
   int sink;
   // optional [Hq]: the sink's score per query head (natural units, not scaled) in place of 0
   const float* sink_values;
+  // the TMA-fed kernel only.  keep_first: with a window, keys at positions below this stay visible (their pages are
+  // walked in front of the window's).  softcap > 0: a score s becomes softcap * tanh(s / softcap) after the scale.
+  int keep_first;
+  float softcap;
 };
 
 __device__ __forceinline__ float2 unpack_bf162(unsigned r) {

@@ -184,7 +184,7 @@ __device__ __forceinline__ void dt_load_query(const DecodeMmaArgs& a, int b, int
 // beyond the context are masked (keys) and zeroed (values).
 template <int D, bool FUSED>
 __device__ __forceinline__ void dt_page_step(const DecodeMmaArgs& a, unsigned char* stage, int p, int ctx, int first_key,
-                                             int pages_total, bool owns_new_row, const int* table, int kvh,
+                                             int kept, int pages_total, bool owns_new_row, const int* table, int kvh,
                                              __nv_bfloat16 new_k0, __nv_bfloat16 new_k1, unsigned new_v,
                                              const unsigned (&qf)[D / 16][4], float (&o)[D / 8][4], float (&m_run)[2],
                                              float (&l_run)[2]) {
@@ -256,9 +256,11 @@ __device__ __forceinline__ void dt_page_step(const DecodeMmaArgs& a, unsigned ch
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float v = (s_acc[n][i] + s_odd[n][i]) * a.scale;
+      // a capped score: cap * tanh(v / cap), tanh(x) = 1 - 2 / (1 + e^(2x)) on the fast exponential and division
+      if (a.softcap > 0.f) v = a.softcap * (1.f - __fdividef(2.f, 1.f + __expf(2.f * v / a.softcap)));
       if (edge) {
         const int kpos = p * MLL_PAGE + warp * 16 + n * 8 + 2 * t + (i & 1);
-        if (!(kpos < ctx && kpos >= first_key)) v = -INFINITY;
+        if (!(kpos < ctx && (kpos >= first_key || kpos < kept))) v = -INFINITY;
       }
       s_acc[n][i] = v;
       tile_max[i >> 1] = fmaxf(tile_max[i >> 1], v);
@@ -351,8 +353,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   const int first_page = first_key / MLL_PAGE;
   // a sequence uses as many of the offered splits as its own length pays for (attention_decode.cuh)
   // ... or as many as its entry of the work list says
-  const int n_eff = listed ? min(entry >> 24, max(1, pages_total - first_page))
-                           : decode_splits_for(pages_total - first_page, a.n_splits);
+  // kept first tokens in front of the window: their pages come first in the walk, whose step w stands for page w below
+  // n_kept and for page first_page + (w - n_kept) from there on
+  const int kept = (a.window > 0 && a.keep_first > 0) ? min(a.keep_first, first_key) : 0;
+  const int n_kept = min((kept + MLL_PAGE - 1) / MLL_PAGE, first_page);
+  const int walk_total = n_kept + pages_total - first_page;
+  const int n_eff = listed ? min(entry >> 24, max(1, walk_total)) : decode_splits_for(walk_total, a.n_splits);
   const bool misplaced = (ring & 1023u) != 0;  // cannot hold swizzled tiles: report, and do no work (uniform for the block)
   if (misplaced && tid == 0) atomicExch(&mll_attn_decode_tma_error_flag, 2);
   // splits beyond the sequence's own count have no work; in a cluster they still meet the others at its barriers
@@ -367,10 +373,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
   float* merged_l = merged_m + 16;
   bool failed = true;
   if (active) {
-    const int per_split = (pages_total - first_page + n_eff - 1) / n_eff;
-    const int p_begin = first_page + split * per_split;
-    const int p_end = min(pages_total, p_begin + per_split);
-    const int n_pages = max(0, p_end - p_begin);
+    const int per_split = (walk_total + n_eff - 1) / n_eff;
+    const int w_begin = split * per_split;
+    const int w_end = min(walk_total, w_begin + per_split);
+    const int n_pages = max(0, w_end - w_begin);
+    auto page_at = [&](int w) { return w < n_kept ? w : first_page + (w - n_kept); };
     const int* table = a.block_table + (size_t)a.seq_slot[b] * a.max_blocks;
 
     if (tid == 0) {
@@ -395,13 +402,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
     if (warp == 4) {
       // ---- producer ---------------------------------------------------------------------------- //
       if (lane == 0 && n_pages > 0) {
-        int page = table[p_begin];
+        int page = table[page_at(w_begin)];
         for (int it = 0; it < n_pages; ++it) {
           const int st = it % DT_STAGES;
           dt_mbar_wait(empty + 8 * st, ((it / DT_STAGES) & 1) ^ 1, abort_flag);  // the stage's previous use (none in the first round)
           if (*abort_flag) break;
           const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
-          if (it + 1 < n_pages) page = table[p_begin + it + 1];  // looked up while this page's loads fly
+          if (it + 1 < n_pages) page = table[page_at(w_begin + it + 1)];  // looked up while this page's loads fly
           asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full + 8 * st), "r"((unsigned)L::STAGE)
                        : "memory");
           const unsigned dst = ring + st * L::STAGE;
@@ -421,8 +428,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
 
       // FUSED: the block whose pages include the sequence's last one fetches the new key pair and
       // value pair of its kv head now (one pair per thread), long before the page comes up
-      const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && p_begin <= pages_total - 1 &&
-                                pages_total - 1 < p_end;
+      const bool owns_new_row = FUSED && a.k_write != nullptr && ctx > 0 && w_begin <= walk_total - 1 &&
+                                walk_total - 1 < w_end;  // the sequence's last page ends the walk
       __nv_bfloat16 new_k0 = __float2bfloat16_rn(0.f), new_k1 = new_k0;
       unsigned new_v = 0;
       if (owns_new_row && tid < D / 2) dt_fetch_new_row<D>(a, b, kvh, ctx, tid, new_k0, new_k1, new_v);
@@ -431,10 +438,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_co
       dt_load_query<D, FUSED>(a, b, h0, ng, ctx, g, t, qf);
 
       for (int it = 0; it < n_pages; ++it) {
-        const int p = p_begin + it;
+        const int p = page_at(w_begin + it);
         const int st = it % DT_STAGES;
         dt_mbar_wait(full + 8 * st, (it / DT_STAGES) & 1, abort_flag);
-        dt_page_step<D, FUSED>(a, smem_raw + st * L::STAGE, p, ctx, first_key, pages_total, owns_new_row, table, kvh,
+        dt_page_step<D, FUSED>(a, smem_raw + st * L::STAGE, p, ctx, first_key, kept, pages_total, owns_new_row, table, kvh,
                                new_k0, new_k1, new_v, qf, o, m_run, l_run);
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
@@ -649,7 +656,7 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                                 float* scratch, void* out, int n_seqs, int n_heads, int n_kv_heads, int head_dim,
                                 int max_blocks, int n_splits, int window, float scale, int* counters,
                                 int cluster_merge, const int* seq_order, const int* work, int work_pairs, int sink,
-                                const float* sink_values, cudaStream_t stream) {
+                                const float* sink_values, int keep_first, float softcap, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_decode_tma_supported(MLL_BF16, head_dim), "attention decode (tma): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention decode (tma): bad head counts");
   MLL_REQUIRE(n_seqs >= 0 && n_splits >= 1 && n_splits <= 65535, "attention decode (tma): bad batch or split count");
@@ -678,6 +685,10 @@ MLL_API int mll_attn_decode_tma(const void* q, const void* qkv, int qkv_ld, cons
                        fused && write_kv ? (__nv_bfloat16*)v_cache : nullptr, qkv_ld, interleaved, seq_order, work};
   a.sink = (sink || sink_values) ? 1 : 0;
   a.sink_values = sink_values;
+  MLL_REQUIRE(keep_first >= 0 && softcap >= 0.f && (keep_first == 0 || window > 0),
+              "attention decode (tma): kept first tokens need a window; no negative cap");
+  a.keep_first = keep_first;
+  a.softcap = softcap;
   const int rows = work != nullptr ? work_pairs : n_seqs;  // the grid's second index
   if (head_dim == 64)
     return fused ? mll::launch_decode_tma<64, true>(kmap, vmap, a, rows, cluster_merge, stream)

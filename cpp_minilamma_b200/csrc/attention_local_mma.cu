@@ -44,6 +44,10 @@ struct LocalMmaArgs {
   float scale;                   // the scale in natural units (scale_log2 = scale * log2 e)
 };
 
+// tanh(x) = 1 - 2 / (1 + e^(2x)) on the fast exponential and division: absolute error near 1e-6, which a capped score
+// (cap * tanh) of a bfloat16 run does not see; large |x| saturates to +-1 (e^(2x) overflows to infinity or falls to 0).
+__device__ __forceinline__ float fast_tanh(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
+
 template <int DK, int DV>
 struct LocalMmaSmem {
   static constexpr int KS = DK + 8, VS = DV + 8;
@@ -146,6 +150,9 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     }
   }
 
+  const float cap_log2 = a.softcap * 1.4426950408889634f, scale_over_cap = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
+  // single tokens: a warp whose 16 rows lie past the group's heads has nothing to compute; it still loads and waits
+  const bool idle = by_heads && warp * 16 >= rows;
   for (int w = pb; w <= pe; ++w) {
     const int p = page_at(w);
     const int stage = (w - pb) & 1;
@@ -162,6 +169,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     cp_async_commit();
     const __nv_bfloat16* kt = kv_s + (size_t)stage * stage_elems;
     const __nv_bfloat16* vt = v_in_k ? kt : kt + L::KTILE;
+    if (idle) continue;
 
     float s_acc[8][4];
 #pragma unroll
@@ -187,8 +195,7 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float v = a.softcap > 0.f ? a.softcap * 1.4426950408889634f * tanhf(s_acc[n][i] * a.scale / a.softcap)
-                                  : s_acc[n][i] * a.scale_log2;
+        float v = a.softcap > 0.f ? cap_log2 * fast_tanh(s_acc[n][i] * scale_over_cap) : s_acc[n][i] * a.scale_log2;
         if (needs_mask) {
           const int row = warp * 16 + g + ((i >> 1) << 3);
           const int qpos = pos0 + row * pos_step;

@@ -33,6 +33,11 @@
 // microseconds each, 72 instead of 47 us for a 2,048-token prompt, so the caller passes a list of
 // 128-row tiles.
 //
+// A window may keep the sequence's first tokens visible (`keep_first`): the pages that hold them are walked first, then
+// the window's own, and the mask lets a key through if it is inside the window or below `keep_first`.  A capped score,
+// cap * tanh(scale * s / cap), is formed by the softmax threads right after they read S (two more special-function
+// instructions a score: with a cap the softmax, not the tensor pipe, sets the kernel's pace).
+//
 // Every mbarrier wait is bounded; a wait that runs out raises an error flag (read through
 // mll_take_device_error), makes the block's later waits return at once, the block stores nothing,
 // frees its tensor memory and exits.  Every warp-wide tensor-memory instruction sits in warp-uniform
@@ -67,6 +72,9 @@ struct PrefillTc5Args {
   float scale_log2;
   int sink;   // 1: the softmax's denominator has one more term exp(0), which carries no value
   const float* sink_values;  // optional [Hq]: the sink's score per query head (natural units, not scaled) in place of 0
+  int keep_first;            // with a window: keys at positions below this stay visible
+  float scale_over_cap;      // scale / cap, and cap / scale: a raw score s becomes (cap / scale) tanh(s scale / cap),
+  float cap_over_scale;      // which the scale then turns into cap * tanh(..); both 0 without a cap
 };
 
 __device__ __forceinline__ unsigned a_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -343,7 +351,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
   if (a.chunk > 0) first_key = max(first_key, (pos0 / a.chunk) * a.chunk);  // of the tile's first row; later rows reach no further back
   const int last_chunk_start = a.chunk > 0 ? ((pos0 + rows - 1) / a.chunk) * a.chunk : 0;
   const int p_first = first_key / MLL_PAGE, p_last = (pos0 + rows - 1) / MLL_PAGE;
-  const int n_pages = p_last - p_first + 1;
+  // kept first tokens in front of the window: their pages come first in the walk, whose step i stands for page i
+  // below n_kept and for page p_first + (i - n_kept) from there on (the same numbers in every warp)
+  const int kept = (a.window > 0 && a.keep_first > 0) ? min(a.keep_first, first_key) : 0;
+  const int n_kept = min((kept + MLL_PAGE - 1) / MLL_PAGE, p_first);
+  const int n_pages = n_kept + p_last - p_first + 1;
+  auto page_at = [&](int i) { return i < n_kept ? i : p_first + (i - n_kept); };
 
   if (tid == 0) {
     for (int i = 0; i < L::AB_COUNT; ++i)
@@ -369,12 +382,12 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
 #pragma unroll
       for (int b = 0; b < DB; ++b)
         a_tma_load_2d(q_s + b * (A_ROWS * 128), &qmap, h * D + b * 64, qstart + row0, bar(L::AB_Q, 0));
-      int page = table[p_first];
+      int page = table[page_at(0)];
       for (int i = 0; i < n_pages && !*abort_flag; ++i) {
         const int st = i % KS;
         const unsigned parity = ((i / KS) & 1) ^ 1;  // the stage's previous use (none in the first round)
         const int row = (page * a.n_kv_heads + kvh) * MLL_PAGE;
-        if (i + 1 < n_pages) page = table[p_first + i + 1];  // looked up while this page's loads fly
+        if (i + 1 < n_pages) page = table[page_at(i + 1)];  // looked up while this page's loads fly
         wait(bar(L::AB_K_EMPTY, st), parity);
         a_mbar_expect_tx(bar(L::AB_K_FULL, st), L::KV_BYTES);
 #pragma unroll
@@ -463,14 +476,21 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
       a_fence_after();
       float s[MLL_PAGE];
       a_tmem_ld64(tmem_row + sb * MLL_PAGE, s);
-      const int k0 = (p_first + i) * MLL_PAGE;
+      const int k0 = page_at(i) * MLL_PAGE;
+      if (a.cap_over_scale > 0.f) {
+        // tanh(x) = 1 - 2 / (1 + e^(2x)) on the fast exponential and division (absolute error near 1e-6)
+#pragma unroll
+        for (int c = 0; c < MLL_PAGE; ++c)
+          s[c] = a.cap_over_scale * (1.f - __fdividef(2.f, 1.f + __expf(2.f * a.scale_over_cap * s[c])));
+      }
       const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS || k0 < last_chunk_start;
       const int chunk_first = a.chunk > 0 ? (qpos / a.chunk) * a.chunk : 0;
       if (needs_mask) {
 #pragma unroll
         for (int c = 0; c < MLL_PAGE; ++c) {
           const int kpos = k0 + c;
-          const bool keep = r < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window) && kpos >= chunk_first;
+          const bool keep = r < rows && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window || kpos < a.keep_first) &&
+                            kpos >= chunk_first;
           s[c] = keep ? s[c] : -INFINITY;
         }
       }
@@ -626,12 +646,14 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
                                  const int* tile_row0, const int* block_table, void* out, int n_tokens,
                                  long long n_pages, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
                                  int max_blocks, int window, int chunk, float scale, int sink,
-                                 const float* sink_values, cudaStream_t stream) {
+                                 const float* sink_values, int keep_first, float softcap, cudaStream_t stream) {
   MLL_REQUIRE(mll_attn_prefill_tc5_supported(MLL_BF16, head_dim), "attention prefill (tcgen05): head_dim %d", head_dim);
   MLL_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention prefill (tcgen05): bad head counts");
   MLL_REQUIRE(n_tiles >= 0 && n_tokens >= 0 && (long long)n_tiles * n_heads < (1ll << 31),
               "attention prefill (tcgen05): bad tile or head count");
   MLL_REQUIRE(window >= 0 && chunk >= 0, "attention prefill (tcgen05): negative window or chunk");
+  MLL_REQUIRE(keep_first >= 0 && softcap >= 0.f && (keep_first == 0 || chunk == 0) && (softcap == 0.f || scale > 0.f),
+              "attention prefill (tcgen05): bad kept tokens or cap");
   MLL_REQUIRE(n_pages > 0 && n_pages * n_kv_heads * MLL_PAGE < (1ll << 31),
               "attention prefill (tcgen05): %lld pages are more than the row coordinate holds", n_pages);
   MLL_REQUIRE(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16 == 0,
@@ -643,7 +665,8 @@ MLL_API int mll_attn_prefill_tc5(const void* q, const void* k_cache, const void*
   if (mll::tensor_map_bf16(v_cache, n_pages * n_kv_heads * MLL_PAGE, head_dim, MLL_PAGE, &vmap) != 0) return -1;
   mll::PrefillTc5Args a{seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0, block_table,
                         (__nv_bfloat16*)out, n_heads, n_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f,
-                        (sink || sink_values) ? 1 : 0, sink_values};
+                        (sink || sink_values) ? 1 : 0, sink_values, keep_first, softcap > 0.f ? scale / softcap : 0.f,
+                        softcap > 0.f ? softcap / scale : 0.f};
   if (head_dim == 64) return mll::launch_prefill_tc5<64>(qmap, kmap, vmap, a, n_tiles, stream);
   return mll::launch_prefill_tc5<128>(qmap, kmap, vmap, a, n_tiles, stream);
 }

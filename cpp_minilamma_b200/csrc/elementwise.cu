@@ -216,9 +216,10 @@ __global__ void swiglu_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out
     float g[8], u[8], r[8];
     Pack8<T>::load(gp, g);
     Pack8<T>::load(up, u);
-    if (bias) {
-      const float* gb = bias + (gp - row);
-      const float* ub = bias + (up - row);
+    if (bias) {  // groups of 8 floats start on 32-byte boundaries of the bias (the launch checks its base)
+      float gb[8], ub[8];
+      Pack8<float>::load(bias + (gp - row), gb);
+      Pack8<float>::load(bias + (up - row), ub);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         g[i] += gb[i];
@@ -486,7 +487,7 @@ MLL_API int mll_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
   if (n_tokens == 0) return 0;
   const int threads = 256;
   const bool vec = inter % 8 == 0 && (block == 0 || block == 8) && ((uintptr_t)gu % 16 == 0) &&
-                   ((uintptr_t)out % 16 == 0);
+                   ((uintptr_t)out % 16 == 0) && ((uintptr_t)bias % 16 == 0);
   if (vec) {
     long long groups = ((long long)n_tokens * (inter / 8) + threads - 1) / threads;
     if (groups > mll_sm_count() * 32) groups = mll_sm_count() * 32;

@@ -715,6 +715,12 @@ def _check_sink_values(sink_values, n_heads: int) -> None:
             raise KernelError(f"attention: {sink_values.shape[0]} sink values for {n_heads} heads")
 
 
+def attention_decode_takes_window_extras(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether `attention_decode` would run the kernel that knows kept first tokens and capped scores."""
+    return bool(USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and dtype == torch.bfloat16
+                and lib().mll_attn_decode_tma_supported(dtype_code(dtype), head_dim))
+
+
 USE_TENSOR_CORE_PREFILL = True
 USE_TCGEN05_PREFILL = True      # off: the mma.sync kernel takes the tensor-core prefill
 
@@ -723,8 +729,10 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
                      n_heads: int, n_kv_heads: int, head_dim: int, n_splits: int, window: int,
                      scale: float, counters: Optional[torch.Tensor] = None, order: Optional[torch.Tensor] = None,
                      work: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False,
-                     sink_values: Optional[torch.Tensor] = None) -> None:
+                     sink_values: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: float = 0.0) -> None:
     """One query token per sequence (q row i belongs to sequence i) over the paged cache.
+    `keep_first` (with a window) and `softcap`: the TMA-fed kernel only (ask `attention_decode_takes_window_extras`
+    first) - keys below `keep_first` stay visible; a score s becomes softcap * tanh(s / softcap) after the scale.
     `sink` (bfloat16 tensor-core kernels only): one more term exp(0) in the softmax's denominator, or
     exp(sink_values[head]) with `sink_values` (float32 [Hq], not scaled).
     `chunk` > 0 (not together with a window): the query sees the keys of its own chunk of that many positions only,
@@ -757,8 +765,10 @@ def attention_decode(q, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratc
     if q.dtype == torch.bfloat16 and _tma_decode(q, None, None, None, False, False, k_cache, v_cache, seq_slot, seq_ctx,
                                                 block_table, scratch, out, n_seqs, n_heads, n_kv_heads, head_dim,
                                                 n_splits, window, scale, counters, _order(order, n_seqs), work,
-                                                sink=sink, sink_values=sink_values):
+                                                sink=sink, sink_values=sink_values, keep_first=keep_first, softcap=softcap):
         return
+    if keep_first or softcap:
+        raise KernelError("attention decode: only the TMA-fed kernel keeps first tokens or caps scores")
     if work is not None:
         raise KernelError("attention decode: a work list was given, but the kernel that takes one does not run here")
     if USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_mma_supported(code, head_dim):
@@ -818,7 +828,8 @@ def _work(work, n_seqs: int, n_splits: int):
 
 def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_slot, seq_ctx, block_table, scratch, out,
                 n_seqs, n_heads, n_kv_heads, head_dim, n_splits, window, scale, counters, order=None, work=None,
-                sink: bool = False, sink_values: Optional[torch.Tensor] = None) -> bool:
+                sink: bool = False, sink_values: Optional[torch.Tensor] = None, keep_first: int = 0,
+                softcap: float = 0.0) -> bool:
     """Runs the TMA-fed decode kernel when it takes the problem (bfloat16, head_dim 64/128, arrival
     counters whenever the context is split); returns whether it did."""
     if not (USE_TMA_DECODE and USE_TENSOR_CORE_DECODE and lib().mll_attn_decode_tma_supported(dtype_code(out.dtype), head_dim)):
@@ -835,7 +846,7 @@ def _tma_decode(q, qkv, cos, sin, interleaved, write_kv, k_cache, v_cache, seq_s
                                      ctypes.c_float(scale), _ptr(counters if n_splits > 1 else None),
                                      ctypes.c_int(int(USE_CLUSTER_MERGE)), _ptr(order), _ptr(work),
                                      ctypes.c_int(work.shape[0] if work is not None else 0), ctypes.c_int(int(sink)),
-                                     _ptr(sink_values), _stream()),
+                                     _ptr(sink_values), ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
            "attention_decode (TMA, work list)" if work is not None
            else "attention_decode (TMA, cluster merge)" if USE_CLUSTER_MERGE and 2 <= n_splits <= 16
            else "attention_decode (TMA)")
@@ -932,13 +943,15 @@ def attention_prefill_takes_chunks(dtype: torch.dtype, head_dim: int) -> bool:
 def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_qlen, tile_seq, tile_row0,
                       block_table, out, n_tiles: int, n_heads: int, n_kv_heads: int, head_dim: int,
                       window: int, scale: float, wide_tiles=None, chunk: int = 0, sink: bool = False,
-                      sink_values: Optional[torch.Tensor] = None) -> None:
+                      sink_values: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: float = 0.0) -> None:
     """Tiles of up to 64 query tokens of sequences with unequal lengths over the paged cache.
     `wide_tiles`: (sequence, first row) int32 lists of the same rows in tiles of 128, which the tcgen05 kernel
     works on; without them it walks the 64-row list and every other block finds nothing to do.
     `chunk` > 0 (the tcgen05 kernel only; ask `attention_prefill_takes_chunks` first): key j is visible from query i
     only if j // chunk == i // chunk.  `sink` (the same kernel only): one more term exp(0) in the softmax's denominator,
-    or exp(sink_values[head]) with `sink_values` (float32 [Hq], not scaled)."""
+    or exp(sink_values[head]) with `sink_values` (float32 [Hq], not scaled).  `keep_first` (with a window) and
+    `softcap` (the same kernel only): keys below `keep_first` stay visible; a score s becomes softcap * tanh(s / softcap)
+    after the scale."""
     _check_attention(q, k_cache, v_cache, out, n_heads, n_kv_heads, head_dim)
     _check_sink_values(sink_values, n_heads)
     sink = bool(sink or sink_values is not None)
@@ -963,11 +976,12 @@ def attention_prefill(q, k_cache, v_cache, seq_slot, seq_ctx, seq_qstart, seq_ql
                                           ctypes.c_longlong(k_cache.shape[0]), ctypes.c_int(n_tiles),
                                           ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(head_dim),
                                           ctypes.c_int(block_table.shape[1]), ctypes.c_int(window), ctypes.c_int(chunk),
-                                          ctypes.c_float(scale), ctypes.c_int(int(sink)), _ptr(sink_values), _stream()),
+                                          ctypes.c_float(scale), ctypes.c_int(int(sink)), _ptr(sink_values),
+                                          ctypes.c_int(keep_first), ctypes.c_float(softcap), _stream()),
                "attention_prefill (tcgen05)")
         return
-    if chunk or sink:
-        raise KernelError("attention prefill: only the tcgen05 kernel masks by chunks or has a sink")
+    if chunk or sink or keep_first or softcap:
+        raise KernelError("attention prefill: only the tcgen05 kernel masks by chunks, has a sink, keeps first tokens or caps scores")
     if USE_TENSOR_CORE_PREFILL and lib().mll_attn_prefill_mma_supported(dtype_code(q.dtype), head_dim):
         _check(lib().mll_attn_prefill_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seq_slot), _ptr(seq_ctx),
                                           _ptr(seq_qstart), _ptr(seq_qlen), _ptr(tile_seq), _ptr(tile_row0),

@@ -203,25 +203,29 @@ struct SsdPrepArgs {
   int ld, n_heads, n_groups, d, dv, taps;
 };
 
-// grid (tokens), 256 threads; dynamic shared memory: H floats (dt per head).
+// grid (tokens, pieces of the channels), 256 threads, a channel a thread; dynamic shared memory: H floats (dt per head).
+// A block forms the step sizes of the heads whose x-channels it holds; the blocks of piece 0 also write the decays.
 template <typename T>
-__global__ void __launch_bounds__(256) ssd_prepare_kernel(SsdPrepArgs a) {
+__global__ void __launch_bounds__(256) ssd_prepare_kernel(SsdPrepArgs a, int per_block) {
   extern __shared__ float dt_s[];
   const int t = blockIdx.x;
   const int H = a.n_heads, G = a.n_groups, d = a.d, dv = a.dv, taps = a.taps;
   const int inner = H * dv, gn = G * d, C = inner + 2 * gn;
   const T* proj = (const T*)a.proj;
   const T* row = proj + (size_t)t * a.ld;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+  const int c_begin = blockIdx.y * per_block, c_end = min(C, c_begin + per_block);
+  const int h_begin = blockIdx.y == 0 ? 0 : min(H, c_begin / dv);
+  const int h_end = blockIdx.y == 0 ? H : min(H, (min(c_end, inner) + dv - 1) / dv);
+  for (int h = h_begin + threadIdx.x; h < h_end; h += blockDim.x) {
     const float dt = softplus_f(to_float(row[inner + C + h]) + a.dt_bias[h]);
     dt_s[h] = dt;
-    a.decay[(size_t)t * H + h] = expf(-expf(a.a_log[h]) * dt);
+    if (blockIdx.y == 0) a.decay[(size_t)t * H + h] = expf(-expf(a.a_log[h]) * dt);
   }
   __syncthreads();
   const int seq = a.tok_seq[t];
   const int local = t - a.seq_qstart[seq];  // index among this step's tokens of the sequence
   const float* state = a.conv_state + (size_t)a.seq_slot[seq] * (taps - 1) * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = c_begin + threadIdx.x; c < c_end; c += blockDim.x) {
     float y = a.conv_b[c];
     for (int back = 0; back < taps; ++back) {  // the input `back` tokens ago meets tap taps - 1 - back
       float x;
@@ -567,10 +571,14 @@ MLL_API int mll_ssd_prepare(const void* proj, const float* conv_w, const float* 
   mll::SsdPrepArgs a{proj, conv_w, conv_b, conv_state, a_log, dt_bias, tok_seq, seq_slot, seq_qstart, q, k, u, xs, decay,
                      ld, n_heads, n_groups, d, dv, taps};
   const size_t smem = (size_t)n_heads * sizeof(float);
+  const int channels = n_heads * dv + 2 * n_groups * d;
+  const int per_block = 256;  // a channel a thread: enough blocks for a step of a few tokens, no loop for a prompt
+  const dim3 grid(n_tokens, (channels + per_block - 1) / per_block);
+  MLL_REQUIRE(grid.y <= 65535, "ssd prepare: too many channels for one launch");
   if (dtype == MLL_F32)
-    MLL_LAUNCH((mll::ssd_prepare_kernel<float>), n_tokens, 256, smem, stream, a);
+    MLL_LAUNCH((mll::ssd_prepare_kernel<float>), grid, 256, smem, stream, a, per_block);
   else if (dtype == MLL_BF16)
-    MLL_LAUNCH((mll::ssd_prepare_kernel<__nv_bfloat16>), n_tokens, 256, smem, stream, a);
+    MLL_LAUNCH((mll::ssd_prepare_kernel<__nv_bfloat16>), grid, 256, smem, stream, a, per_block);
   else
     MLL_REQUIRE(false, "ssd prepare: unknown dtype %d", dtype);
   MLL_LAUNCH_CHECK();

@@ -217,14 +217,15 @@ class ChunkedAttention(Mixer):
         learned = self.sink_values  # a sink with a score of its own per head, or None
         extra = {"keep_first": self.keep_first, "softcap": self.softcap}
         plain = not self.keep_first and not self.softcap  # what the Llama attention's kernels know
-        if (plain and step.all_decode and self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+        if ((plain or K.attention_decode_takes_window_extras(act, self.d)) and step.all_decode and self.d == self.dv
+                and self.d % 16 == 0 and 16 <= self.d <= 256
                 and not (self.chunk and self.window) and act == torch.bfloat16
                 and (not self.sink or K.USE_TENSOR_CORE_DECODE)):
             # single tokens, keys and values of one head size: the Llama attention's decode kernels (TMA-fed or
             # mma.sync), which take the chunk as the key range's start; one block per (sequence, kv head)
             K.attention_decode(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, cache.block_table, None, out,
                                step.n_seqs, self.n_heads, self.n_kv_heads, self.d, 1, self.window, self.scale,
-                               chunk=self.chunk, sink=self.sink, sink_values=learned)
+                               chunk=self.chunk, sink=self.sink, sink_values=learned, **extra)
             return
         if step.all_decode and self._tensor_cores():
             # single tokens that the kernels above do not take (a sink, values of another size): the tensor-core
@@ -239,14 +240,14 @@ class ChunkedAttention(Mixer):
                                     sink_values=learned, **extra)
             return
         tiles = step.meta.get(self.step_metadata_key()) if not step.all_decode else None
-        if plain and tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
+        if tiles and self.d == self.dv and K.attention_prefill_takes_chunks(act, self.d):
             # keys and values of one head size that the Llama attention's tcgen05 prompt kernel takes: that kernel,
             # which knows the chunk mask too
             K.attention_prefill(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,
                                 tiles["tile_seq"], tiles["tile_row0"], cache.block_table, out,
                                 tiles["tile_seq"].shape[0], self.n_heads, self.n_kv_heads, self.d, self.window,
                                 self.scale, wide_tiles=(tiles["wide_seq"], tiles["wide_row0"]), chunk=self.chunk,
-                                sink=self.sink, sink_values=learned)
+                                sink=self.sink, sink_values=learned, **extra)
             return
         if tiles and self._tensor_cores():
             K.local_attention_tiles(q, cache.k, cache.v, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen,

@@ -392,6 +392,24 @@ def test_window_attention_kernels_at_the_edges(dtype, H, G, d, dv, window, keep,
             K.local_attention_heads(q1, kd, vd, one.seq_slot, one.seq_ctx, one.seq_qstart, one.seq_qlen, td, o1, 3, H, G,
                                     d, dv, 0, window, scale, n_splits=splits, scratch=scratch, keep_first=keep, softcap=cap)
             check(o1, last, f"single-token kernel, {splits} splits")
+        if d == dv and K.attention_prefill_takes_chunks(dtype, d):
+            # the tcgen05 prompt kernel (tiles of 128 rows) and the TMA-fed single-token kernel, whole and in splits
+            wide = [(i, row0) for i in range(3) for row0 in range(0, lens[i], 2 * K.PREFILL_TILE)]
+            wide_seq = torch.tensor([i for i, _ in wide], dtype=torch.int32, device=dev)
+            wide_row0 = torch.tensor([r for _, r in wide], dtype=torch.int32, device=dev)
+            out.zero_()
+            K.attention_prefill(qd, kd, vd, step.seq_slot, step.seq_ctx, step.seq_qstart, step.seq_qlen, tiles["tile_seq"],
+                                tiles["tile_row0"], td, out, tiles["tile_seq"].shape[0], H, G, d, window, scale,
+                                wide_tiles=(wide_seq, wide_row0), keep_first=keep, softcap=cap)
+            check(out, slice(0, T), "tcgen05 prompt kernel")
+        if d == dv and K.attention_decode_takes_window_extras(dtype, d):
+            for splits in (1, 3):
+                o1 = torch.zeros((3, H * dv), dtype=dtype, device=dev)
+                scratch = torch.empty(K.attention_decode_scratch_floats(3, H, d, splits), dtype=torch.float32, device=dev)
+                counters = torch.zeros((3 * G * -(-(H // G) // 16),), dtype=torch.int32, device=dev)
+                K.attention_decode(q1, kd, vd, one.seq_slot, one.seq_ctx, td, scratch if splits > 1 else None, o1, 3, H, G, d,
+                                   splits, window, scale, counters=counters if splits > 1 else None, keep_first=keep, softcap=cap)
+                check(o1, last, f"TMA-fed single-token kernel, {splits} splits")
 
 
 @pytest.mark.parametrize("H,G,d,dv,seqs", [(4, 2, 12, 8, 2), (2, 1, 64, 32, 3), (8, 8, 128, 64, 2), (3, 3, 10, 6, 1),

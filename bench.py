@@ -577,6 +577,7 @@ def badolix_rooflines(size, tokens, batch, context, peaks):
     causal = tokens * (tokens + 1) // 2
     seen = sum(min(i + 1, 1024 + 64) for i in range(tokens))            # keys a prompt token sees: its window and the kept tokens
     out["badolix", "prefill", "local_attention_mma (window)"] = ("tensor", 2.0 * H * seen * 2 * d)
+    out["badolix", "prefill", "attention_prefill"] = ("tensor", 2.0 * H * seen * 2 * d)
     out["badolix", "prefill", "local_attention_mma"] = ("tensor", 2.0 * H * causal * (row + rank))
     qkv = (H * d + 2 * G * d) * 2
     for kind, n, seqs in (("prefill", tokens, 1), ("decode", batch, batch)):
@@ -596,6 +597,7 @@ def badolix_rooflines(size, tokens, batch, context, peaks):
         out["badolix", kind, "conv_state_update"] = ("hbm", seqs * (taps - 1) * (inner + 2 * gn) * (2 + 4))
     visible = min(context, 1024 + 64)
     out["badolix", "decode", "local_attention_heads (window)"] = ("hbm", batch * visible * G * 2 * d * 2)
+    out["badolix", "decode", "attention_decode"] = ("hbm", batch * visible * G * 2 * d * 2)
     out["badolix", "decode", "local_attention_heads"] = ("hbm", batch * context * row * 2)
     out["badolix", "prefill", "moe_gate_up_mma"] = ("tensor", 2.0 * tokens * top * 2 * eff * D)
     out["badolix", "prefill", "moe_down_mma"] = ("tensor", 2.0 * tokens * top * eff * D)

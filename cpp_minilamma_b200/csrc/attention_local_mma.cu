@@ -189,7 +189,9 @@ __global__ void __launch_bounds__(128) local_prefill_mma_kernel(LocalMmaArgs a) 
       }
     }
     // mask where the page meets the diagonal, a chunk's or the window's edge, or the tile's end
-    const bool needs_mask = (p * MLL_PAGE + MLL_PAGE - 1 > pos0 + warp * 16 * pos_step) || a.window > 0 || rows < 64 ||
+    // ... or the window's far edge: keys at or below the last row's edge that are not all kept first tokens
+    const bool window_edge = a.window > 0 && p * MLL_PAGE <= last_pos - a.window && p * MLL_PAGE + MLL_PAGE - 1 >= a.keep_first;
+    const bool needs_mask = (p * MLL_PAGE + MLL_PAGE - 1 > pos0 + warp * 16 * pos_step) || window_edge || rows < 64 ||
                             p * MLL_PAGE < last_chunk_start;
 #pragma unroll
     for (int n = 0; n < 8; ++n)

@@ -483,7 +483,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_c
         for (int c = 0; c < MLL_PAGE; ++c)
           s[c] = a.cap_over_scale * (1.f - __fdividef(2.f, 1.f + __expf(2.f * a.scale_over_cap * s[c])));
       }
-      const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || a.window > 0 || rows < A_ROWS || k0 < last_chunk_start;
+      // a page needs the mask where it meets the diagonal, the tile's end, a chunk's start, or the window's far edge: keys
+      // at or below the last row's edge that are not all kept first tokens (a page inside every row's window does not)
+      const bool window_edge = a.window > 0 && k0 <= pos0 + rows - 1 - a.window && k0 + MLL_PAGE - 1 >= a.keep_first;
+      const bool needs_mask = (k0 + MLL_PAGE - 1 > pos0) || window_edge || rows < A_ROWS || k0 < last_chunk_start;
       const int chunk_first = a.chunk > 0 ? (qpos / a.chunk) * a.chunk : 0;
       if (needs_mask) {
 #pragma unroll

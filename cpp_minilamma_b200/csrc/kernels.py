@@ -1487,8 +1487,8 @@ def moe_route(h, w, bias, chosen, weight, top: int, logits: Optional[torch.Tenso
     weight [T, top] (float32) = softmax over the chosen logits.  `logits`: float32 [T, E] = h w^T when the caller
     has formed the product already (a library product over many tokens).
     `all_scores`: s = softmax(w h) over every expert, the choice goes by s + bias, weight = the chosen s over their
-    sum (+ 1e-20), times `scale`.  `groups` = (count, kept): s = sigmoid(w h); the experts form `count` equal groups
-    of neighbours, a group scores the sum of its two largest s, only experts of the `kept` best groups can be chosen;
+    sum (+ 1e-20), times `scale`.  `groups` = (count, kept): s = sigmoid(w h); the experts are cut into `count` runs of
+    consecutive experts of one length, a run is rated by its top two s added up, only experts of the `kept` best-rated runs can be chosen;
     weight as with `all_scores`.  `gate_out` (float32 [T]): w (and logits) have one more row behind the experts';
     the sigmoid of its product with the token goes there."""
     _need(h, "moe route h", None, 2)

@@ -29,9 +29,9 @@ namespace mll {
 // all_scores 1: softmax over every expert; the choice goes by score + bias, the weights are the chosen scores over
 // their sum, times `scale`.  gate_out: the router's matrix has one more row behind the experts'; the sigmoid of its
 // product with the token goes to gate_out[t] (a per-token gate of another part that reads the same rows).
-// all_scores 2: scores = sigmoid of every logit; the experts form `groups` equal groups of neighbours, a group scores
-// the sum of its two largest scores (its one score if it has one expert), and only experts of the `groups_kept` best
-// groups can be chosen (ties: the lower group); the weights are the chosen scores over their sum, times `scale`.
+// all_scores 2: scores = sigmoid of every logit; the experts are cut into `groups` runs of consecutive experts of one
+// length, a run is rated by its top two scores added up (by its one score if it holds one expert), and only experts of
+// the `groups_kept` best-rated runs can be chosen (ties: the lower run); the weights are the chosen scores over their sum, times `scale`.
 struct RouteForm {
   int all_scores;
   float scale;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h,
       for (int e = lane; e < n_experts; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
       __syncwarp();
       for (int g = lane; g < form.groups; g += 32) {
-        float a = -INFINITY, b = -INFINITY;  // the group's two largest scores
+        float a = -INFINITY, b = -INFINITY;  // the run's top two scores
         for (int e = g * per; e < (g + 1) * per; ++e) {
           const float v = z[e];
           if (v > a) { b = a; a = v; } else if (v > b) { b = v; }

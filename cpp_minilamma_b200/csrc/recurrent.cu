@@ -538,16 +538,43 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
   const float* orow = o + (size_t)t * width + c0;
   const float* xrow = xs ? xs + (size_t)t * width + c0 : nullptr;
   const GateT* grow = gate + (size_t)t * gate_ld + c0;
+  // a part of up to 8 x 256 columns stays in registers between the sum and the scaling: one pass over the inputs
+  constexpr int KEEP = 8;
+  const bool kept = n <= KEEP * 256;
+  float held[KEEP];
   float ss = 0.f;
-  for (int e = threadIdx.x; e < n; e += blockDim.x) {
-    float y = orow[e];
-    if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);
-    y *= silu_f(to_float(grow[e]));
-    ss += y * y;
+  if (kept) {
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+      const int e = threadIdx.x + i * 256;
+      float y = 0.f;
+      if (e < n) {
+        y = orow[e];
+        if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);
+        y *= silu_f(to_float(grow[e]));
+      }
+      held[i] = y;
+      ss += y * y;
+    }
+  } else {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      float y = orow[e];
+      if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);
+      y *= silu_f(to_float(grow[e]));
+      ss += y * y;
+    }
   }
   ss = block_sum(ss, scratch);
   const float f = 1.f / sqrtf(ss / (float)n + eps);
   T* dst = out + (size_t)t * width + c0;
+  if (kept) {
+#pragma unroll
+    for (int i = 0; i < KEEP; ++i) {
+      const int e = threadIdx.x + i * 256;
+      if (e < n) dst[e] = from_float<T>(held[i] * f * weight[c0 + e]);
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < n; e += blockDim.x) {
     float y = orow[e];
     if (xrow) y = fmaf(skip[(c0 + e) / dv], xrow[e], y);

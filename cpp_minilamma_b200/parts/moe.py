@@ -8,9 +8,9 @@
 Other forms, each a parameter: scores over all experts (s = softmax(z) over every expert; the choice goes by s + a
 stored correction, the weights are the chosen s over their sum, times a constant); experts without a gate,
 W_down gelu(W_up h); identity experts - the router's last rows belong to experts without tensors, whose output is
-their input times the weight; sigmoid scores with a choice limited to groups (s = sigmoid(z); the experts form equal
-groups of neighbours, a group scores the sum of its two largest s, only experts of the best `keep` groups can be chosen;
-the weights are the chosen s over their sum); a gate on the shared expert, sigmoid(w_g . h), one number per token, whose row rides
+their input times the weight; sigmoid scores with a choice limited to groups (s = sigmoid(z); the experts are cut into
+`count` runs of consecutive experts of one length, a run is rated by its top two s added up, only experts of the `keep`
+best-rated runs can be chosen; the weights are the chosen s over their sum); a gate on the shared expert, sigmoid(w_g . h), one number per token, whose row rides
 behind the router's so that the routing kernel forms it.
 
 The experts' matrices are stacked ([E, 2 I, D] gate rows then up rows, and [E, D, I]); the routing stays on the

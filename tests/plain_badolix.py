@@ -22,8 +22,9 @@ The design in this file's own notation (D model width, T tokens, p positions fro
                      silu; dt = softplus(dt + b_dt); per head S_t = exp(-exp(A_h) dt) S_(t-1) + dt B_t x_t^T,
                      y_t = S_t^T C_t + D_h x_t; y silu(z), normalised in equal parts, times a weight; W_o
   dense ff           W_down (silu(W_gate h + b_g) * (W_up h + b_u)) + b_d
-  routed ff          s = sigmoid(W_r h); experts in equal groups of neighbours, a group scores the sum of its two
-                     largest s, only the best `keep` groups stay; the `top` largest s among them are chosen;
+  routed ff          s = sigmoid(W_r h); the experts are cut into `count` runs of consecutive experts of one length, a
+                     run is rated by its top two s added up, only the `keep` best-rated runs stay open; the `top` highest
+                     s inside them are chosen;
                      weights s_j / (sum of the chosen s + 1e-20); out = sum_j w_j expert_j(h) (experts have no biases)
 """
 from __future__ import annotations

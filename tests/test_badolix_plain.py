@@ -154,7 +154,7 @@ def test_state_space_unrolled_over_earlier_tokens():
 
 def test_routing_inside_the_best_groups():
     s = np.array([0.9, 0.1, 0.2,   0.5, 0.55, 0.0,   0.8, 0.05, 0.3,   0.6, 0.6, 0.6])
-    # group scores (two largest): 1.1, 1.05, 1.1, 1.2 -> groups 3, 0 and (tie with 0 earlier) 2 are kept for keep = 3
+    # ratings of the runs (top two added): 1.1, 1.05, 1.1, 1.2 -> groups 3, 0 and (tie with 0 earlier) 2 are kept for keep = 3
     chosen, weights, margin = pb.route(s, 4, 4, 3)
     assert list(chosen) == [0, 6, 9, 10]          # 0.9, 0.8, then the first two of the tied 0.6s; group 1 is shut out
     assert np.allclose(weights, np.array([0.9, 0.8, 0.6, 0.6]) / 2.9) and np.isclose(margin, 0.0)

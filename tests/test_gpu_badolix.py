@@ -183,6 +183,37 @@ def test_slots_pages_and_states_used_again(models, name):
     assert all(g.pool.n_free == g.pool.n_pages for g in eng.cache.groups)
 
 
+@pytest.mark.parametrize("seed", list(range(200, 216)))
+def test_configurations_drawn_from_fixed_seeds(seed, tmp_path):
+    """Sixteen configurations that nobody chose by hand, in float32 (the sharp comparison): a whole prompt, and the same
+    prompt cut after 250 tokens and decoded beside a second, shorter request that ends earlier."""
+    cfg = tb.random_config(seed)
+    W = tb.make_weights(cfg, seed)
+    folder = tb.write_folder(cfg, W, tmp_path / "m")
+    W = {k: v.astype(np.float64) for k, v in W.items()}
+    llm = ml.load(folder, dtype="float32", max_tokens=2048, max_positions=512)
+    eng = llm.engine
+    a, b = tb.tokens(cfg, 330, seed + 1), tb.tokens(cfg, 90, seed + 2)
+    ref_a, ref_b = pb.forward(cfg, W, a), pb.forward(cfg, W, b)
+    close(run_alone(llm, a, [len(a)]), ref_a, "float32", f"seed {seed} whole")
+    sa, sb = eng.acquire(2)
+    out = eng.step([StepEntry(sa, a[:250], list(range(250))), StepEntry(sb, b[:40], list(range(40)))]).cpu().numpy()
+    rows_a, rows_b = [out[:250]], [out[250:]]
+    for p in range(250, 330):
+        q = p - 210
+        entries = [StepEntry(sa, [a[p]], [0])] + ([StepEntry(sb, [b[q]], [0])] if q < 90 else [])
+        out = eng.step(entries).cpu().numpy()
+        rows_a.append(out[:1])
+        if q < 90:
+            rows_b.append(out[1:2])
+        if q == 89:
+            eng.release(sb)
+    eng.release(sa)
+    close(np.concatenate(rows_a), ref_a, "float32", f"seed {seed} decoded in a batch")
+    close(np.concatenate(rows_b), ref_b, "float32", f"seed {seed} the shorter request")
+    eng.cache.check()
+
+
 def test_an_engine_cuts_a_long_step_itself(models):
     models("mixed")
     folder, cfg, W = _FOLDERS["mixed"]

@@ -227,3 +227,50 @@ def make_folder(name, folder, seed=0):
 
 def tokens(cfg, length, seed):
     return [int(t) for t in np.random.RandomState(seed).randint(0, cfg["vocab"], size=length)]
+
+
+def random_config(seed):
+    """A configuration drawn from a fixed seed: two to six layers of any kind in any order, sizes from lists that hold
+    tensor-core sizes and others, layers that read an earlier attention layer's keys under a mask of their own, dense,
+    routed and missing feed-forwards."""
+    import random
+    rng = random.Random(seed)
+    layers, owners = [], []
+    for i in range(rng.randint(2, 6)):
+        kind = rng.choice(["attention", "attention", "latent_attention", "mamba2"])
+        if kind == "attention" and owners and rng.random() < 0.4:
+            j = rng.choice(owners)
+            m = dict(layers[j]["mixer"], kv_from=j, scale=rng.choice([0.1, 0.125, 0.2]), softcap=rng.choice([10.0, 30.0, 50.0]),
+                     mask={"size": rng.choice([17, 64, 100, 130, 200]), "keep_first": rng.choice([0, 1, 8, 24, 64, 70])})
+            m["heads"] = m["kv_heads"] * rng.choice([1, 2, 4])
+        elif kind == "attention":
+            d, G = rng.choice([16, 24, 32, 48, 64, 64, 96, 128]), rng.choice([1, 2, 4])
+            m = {"heads": G * rng.choice([1, 2, 4]), "kv_heads": G, "dim": d, "vdim": rng.choice([d, d, d, 32, 64]),
+                 "scale": rng.choice([0.1, 0.125, 0.18, 0.25]), "softcap": rng.choice([10.0, 30.0, 50.0]),
+                 "mask": {"size": rng.choice([17, 64, 100, 130, 200]), "keep_first": rng.choice([0, 1, 8, 24, 64, 70])},
+                 "rot": rot(rng.choice([d, d, d // 2]) // 2 * 2, rng.choice([10000.0, 200000.0]), {"factor": rng.choice([2.0, 4.0, 8.0])})}
+            owners.append(i)
+        elif kind == "latent_attention":
+            r = rng.choice([8, 16, 32])
+            m = {"heads": rng.choice([2, 4, 8]), "dim": rng.choice([16, 32, 64]), "rot_dim": r, "vdim": rng.choice([16, 32, 64]),
+                 "kv_rank": rng.choice([32, 48, 64, 96, 128, 160]), "scale": rng.choice([0.1, 0.15, 0.2]),
+                 "rot": rot(r, rng.choice([10000.0, 1000000.0]), {"factor": rng.choice([4.0, 8.0, 16.0]),
+                                                                  "original": rng.choice([256, 1024, 4096]), "fast": 32.0, "slow": 1.0})}
+        else:
+            G = rng.choice([1, 2, 4])
+            H = G * rng.choice([1, 2, 4])
+            m = {"heads": H, "vdim": rng.choice([16, 32, 64]), "state": rng.choice([16, 32, 64, 128]), "groups": G,
+                 "conv": rng.choice([2, 3, 4]), "norm_groups": rng.choice([1, 2, G, H])}
+        feed = rng.choice(["dense", "moe", "moe", None])
+        if feed == "dense":
+            mlp = dense(rng.choice([64, 128, 256, 200]))
+        elif feed == "moe":
+            count, per = rng.choice([1, 2, 4]), rng.choice([1, 2, 3, 4])
+            keep = rng.randint(1, count)
+            mlp = moe(count * per, rng.randint(1, min(keep * per, 6)), rng.choice([32, 64, 96]), count, keep)
+        else:
+            mlp = None
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    return config(layers, width=rng.choice([64, 96, 128, 160, 192, 256, 384]), vocab=rng.choice([211, 512, 1000]),
+                  eps=rng.choice([1e-5, 1e-6]), embed_scale=rng.choice([1.0, 3.0, 12.0]), mult=rng.choice([0.5, 0.7, 1.0]),
+                  logit_scale=rng.choice([0.5, 1.0, 2.0]))
